@@ -1,0 +1,626 @@
+// Persistent grouped GEMM for sm_100a: bf16 x bf16 -> fp32 on tcgen05 tensor
+// cores with TMEM accumulators, operands staged by (non-multicast) TMA.
+//
+//   C_g[m_g, N] = A_g[m_g, K] * W_g[N, K]^T      for g in [0, G)
+//
+// A is one packed row-major buffer (groups back to back, ragged m_g read from a
+// device array), W is [G*N, K] row-major ("K-major" for both operands).
+//
+// One CTA per SM, warp-specialised:
+//   warp 0      TMA producer (one lane)
+//   warp 1      TMEM owner + MMA issuer (one lane)
+//   warps 2-5   epilogue: TMEM -> registers -> shared staging -> coalesced stores
+//   warps 6-9   (fused-dispatch build only) token senders: gather this rank's
+//               routed rows and store them into the owning rank's receive
+//               buffer over NVLink, then signal the M-tile they landed in.
+//
+// Epilogues: plain store, SiLU-gated (gate/up column blocks interleaved per
+// 256-wide weight tile) and "combine": scale by the row's top-k weight and
+// store straight into the source rank's slot buffer, then count arrivals there.
+//
+// Role of this file relative to the reference project: the persistent grouped
+// GEMM sketched in kernels.py:207-289 / layers/expert.py:6-65, the token
+// exchange of kernels.py:69-146 (fused in as the sender role) and the
+// combine step the reference does not have.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "moe_args.h"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;            // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int STG_COLS = 64;                          // columns per epilogue pass
+constexpr int STG_ROW_BYTES = STG_COLS * 2 + 16;      // padded: conflict-free 16 B stores
+constexpr int STG_BYTES = BM * STG_ROW_BYTES;         // 18 KiB
+constexpr int TMEM_COLS = 512;                        // two 256-column accumulators
+constexpr int NUM_THREADS_PLAIN = 192;
+constexpr int NUM_THREADS_FUSED = 320;
+
+struct __align__(16) ControlSmem {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t drain;
+  uint32_t tmem_base;
+  int abort_flag;
+  int total_mtiles;
+  int total_units;
+  int g_rows[B200_MAX_GROUPS];
+  int g_row_start[B200_MAX_GROUPS + 1];
+  int g_mtile_start[B200_MAX_GROUPS + 1];
+  // sender tables (fused dispatch), indexed by rotated bucket number
+  int b_count[B200_MAX_EXPERTS];       // rows this rank sends to the bucket
+  int b_send_start[B200_MAX_EXPERTS];  // first row of the bucket in send_order
+  int b_dst_row[B200_MAX_EXPERTS];     // first destination row in the peer buffer
+  int b_dst_rel0[B200_MAX_EXPERTS];    // that row relative to the expert's first row
+  int b_dst_mtile0[B200_MAX_EXPERTS];  // index of the expert's first M-tile at the peer
+  int b_dst_rank[B200_MAX_EXPERTS];
+  int b_unit_start[B200_MAX_EXPERTS + 1];
+};
+
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + (int)sizeof(ControlSmem) + 1024;
+static_assert(SMEM_BYTES <= 232448, "exceeds 227 KiB of shared memory per CTA");
+
+// Maps a linear tile index to (group, m-tile, n-tile).  Tiles are ordered per
+// group in chunks of `gm` M-tiles; inside a chunk the M index runs fastest so
+// that concurrently running CTAs share a few weight tiles and a chunk of A
+// that stays resident in L2 while the N index sweeps.
+__device__ __forceinline__ bool decode_tile(const ControlSmem& c, int G, int TN, int gm, int idx,
+                                            int& cursor, int& g, int& m, int& n) {
+  while (cursor < G && idx >= TN * c.g_mtile_start[cursor + 1]) ++cursor;
+  if (cursor >= G) return false;
+  g = cursor;
+  const int tm = c.g_mtile_start[g + 1] - c.g_mtile_start[g];
+  const int j = idx - TN * c.g_mtile_start[g];
+  const int chunk_tiles = gm * TN;
+  const int ch = j / chunk_tiles;
+  const int r = j - ch * chunk_tiles;
+  const int cm = min(gm, tm - ch * gm);
+  n = r / cm;
+  m = ch * gm + (r - n * cm);
+  return true;
+}
+
+// Exclusive scan of g_rows into g_row_start / g_mtile_start by one warp.
+__device__ __forceinline__ void scan_groups(ControlSmem& c, int G, int lane) {
+  int row_carry = 0, tile_carry = 0;
+  for (int base = 0; base < G; base += 32) {
+    const int g = base + lane;
+    const int rows = (g < G) ? c.g_rows[g] : 0;
+    const int tiles = (rows + BM - 1) / BM;
+    int rs = rows, ts = tiles;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int r2 = __shfl_up_sync(0xffffffffu, rs, o);
+      const int t2 = __shfl_up_sync(0xffffffffu, ts, o);
+      if (lane >= o) { rs += r2; ts += t2; }
+    }
+    if (g < G) {
+      c.g_row_start[g] = row_carry + rs - rows;
+      c.g_mtile_start[g] = tile_carry + ts - tiles;
+    }
+    row_carry += __shfl_sync(0xffffffffu, rs, 31);
+    tile_carry += __shfl_sync(0xffffffffu, ts, 31);
+  }
+  if (lane == 0) {
+    c.g_row_start[G] = row_carry;
+    c.g_mtile_start[G] = tile_carry;
+    c.total_mtiles = tile_carry;
+  }
+}
+
+__device__ __forceinline__ float silu_f(float g) { return g * __frcp_rn(1.0f + __expf(-g)); }
+
+// Builds the sender tables and this rank's group sizes from the all-ranks
+// routing counts (counts_all[src][dst][e]).  Runs on every thread of the CTA.
+__device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200_dispatch_args& d,
+                                                      int tid, int nthreads, WaitCtx& w) {
+  const int W = d.world, EL = d.e_local, ET = W * EL, me = d.rank;
+  const int* cnt = d.counts_all;
+  // rows this rank receives per local expert
+  for (int e = tid; e < EL; e += nthreads) {
+    int rows = 0;
+    for (int s = 0; s < W; ++s) rows += __ldcg(cnt + ((s * W + me) * EL + e));
+    c.g_rows[e] = rows;
+  }
+  for (int bi = tid; bi < ET; bi += nthreads) {
+    const int ge = (me * EL + bi) % ET;     // start with this rank's own experts
+    const int dst = ge / EL, e = ge - dst * EL;
+    const int n = __ldcg(cnt + ((me * W + dst) * EL + e));
+    int send_start = 0;
+    for (int q = 0; q < ge; ++q) send_start += __ldcg(cnt + (me * ET + q));
+    int group_start = 0, mtile0 = 0;
+    for (int e2 = 0; e2 < e; ++e2) {
+      int rows = 0;
+      for (int s = 0; s < W; ++s) rows += __ldcg(cnt + ((s * W + dst) * EL + e2));
+      group_start += rows;
+      mtile0 += (rows + BM - 1) / BM;
+    }
+    int within = 0;
+    for (int s = 0; s < me; ++s) within += __ldcg(cnt + ((s * W + dst) * EL + e));
+    c.b_count[bi] = n;
+    c.b_send_start[bi] = send_start;
+    c.b_dst_row[bi] = group_start + within;
+    c.b_dst_rel0[bi] = within;
+    c.b_dst_mtile0[bi] = mtile0;
+    c.b_dst_rank[bi] = dst;
+    // units are (bucket, destination M-tile) pairs; stored un-scanned for now
+    c.b_unit_start[bi + 1] = (n > 0) ? ((within + n - 1) / BM - within / BM + 1) : 0;
+    if (n > 0 && (group_start + within + n > d.cap_rows || n < 0)) {
+      report_status(w.status, ST_OVERFLOW);
+      *w.abort_flag = 1;
+    }
+  }
+}
+
+template <int EPI, bool FUSED>
+__global__ void __launch_bounds__(FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                    const __grid_constant__ CUtensorMap tmap_b, const b200_gemm_args ga,
+                    const b200_dispatch_args da, const b200_combine_args ca) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stage_base = smem;
+  uint8_t* staging = smem + STAGES * STAGE_BYTES;
+  ControlSmem& c = *reinterpret_cast<ControlSmem*>(staging + STG_BYTES);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int nthreads = blockDim.x;
+  const int G = FUSED ? da.e_local : ga.num_groups;
+  const int TN = (ga.N + BN - 1) / BN;
+  const int KB = (ga.K + BK - 1) / BK;
+  const int gm = ga.group_m > 0 ? ga.group_m : 16;
+
+  WaitCtx w;
+  w.abort_flag = &c.abort_flag;
+  w.status = ga.status;
+  w.budget_ns = ga.wait_budget_ns;
+
+  // ---------------------------------------------------------------- set-up
+  if (tid == 0) {
+    c.abort_flag = 0;
+    c.total_units = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&c.full[s], 1);
+      mbar_init(&c.empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&c.tmem_full[a], 1);
+      mbar_init(&c.tmem_empty[a], 128);
+    }
+    mbar_init(&c.drain, 1);
+    fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(&c.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  __syncthreads();
+
+  if constexpr (FUSED) {
+    // every rank's routing counts must have landed before offsets can be built
+    if (tid < da.world) wait_flag_geq(da.counts_flag + tid, da.epoch, w, ST_TIMEOUT_COUNTS);
+    __syncthreads();
+    if (!c.abort_flag) build_dispatch_tables(c, da, tid, nthreads, w);
+    __syncthreads();
+    if (tid == 0) {
+      const int ET = da.world * da.e_local;
+      int acc = 0;
+      c.b_unit_start[0] = 0;
+      for (int b = 0; b < ET; ++b) {
+        acc += c.b_unit_start[b + 1];
+        c.b_unit_start[b + 1] = acc;
+      }
+      c.total_units = acc;
+    }
+    if (blockIdx.x == 0 && tid < da.e_local && da.group_rows_out != nullptr)
+      da.group_rows_out[tid] = c.g_rows[tid];
+  } else {
+    for (int g = tid; g < G; g += nthreads) {
+      int r = ga.group_rows[g];
+      c.g_rows[g] = r < 0 ? 0 : r;
+    }
+  }
+  __syncthreads();
+  if (warp == 0) scan_groups(c, G, lane);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+
+  if constexpr (FUSED) {
+    if (tid == 0 && c.g_row_start[G] > da.cap_rows) {
+      report_status(w.status, ST_OVERFLOW);
+      c.abort_flag = 1;
+    }
+    __syncthreads();
+  }
+
+  const uint32_t tmem_base = c.tmem_base;
+  const int total_tiles = c.total_mtiles * TN;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int cursor = 0, stage = 0;
+      uint32_t phase = 0;
+      int issued = 0;
+      bool ok = !c.abort_flag;
+      for (int idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+        int g, m, n;
+        if (!decode_tile(c, G, TN, gm, idx, cursor, g, m, n)) break;
+        const int row0 = c.g_row_start[g] + m * BM;
+        if constexpr (FUSED) {
+          const uint32_t expect = static_cast<uint32_t>(min(BM, c.g_rows[g] - m * BM));
+          const uint32_t* ready = reinterpret_cast<const uint32_t*>(da.peer_ready[da.rank]) +
+                                  c.g_mtile_start[g] + m;
+          if (!wait_flag_geq(ready, expect, w, ST_TIMEOUT_TILE_READY)) { ok = false; break; }
+          fence_proxy_async();   // peer-written rows are read by the async proxy next
+        }
+        const int brow = g * ga.N + n * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&c.empty[stage], phase ^ 1u, w, ST_TIMEOUT_PIPE_EMPTY)) { ok = false; break; }
+          uint8_t* sa = stage_base + stage * STAGE_BYTES;
+          mbar_expect_tx(&c.full[stage], STAGE_BYTES);
+          tma_load_2d(sa, &tmap_a, &c.full[stage], kb * BK, row0);
+          tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, &c.full[stage], kb * BK, brow);
+          ++issued;
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      // Retire every load still in flight before shared memory is released.
+      const int pending = min(issued, STAGES);
+      for (int i = 0; i < pending; ++i) {
+        // walk back from the most recent issue
+        int s = stage - 1 - i;
+        uint32_t ph = phase;
+        if (s < 0) { s += STAGES; ph ^= 1u; }
+        WaitCtx wd = w;
+        int no_abort = 0;
+        wd.abort_flag = &no_abort;   // drain even when the CTA has given up
+        mbar_wait(&c.full[s], ph, wd, ST_TIMEOUT_DRAIN);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_bf16_f32(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = !c.abort_flag;
+      for (int idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(&c.tmem_empty[acc], acc_phase ^ 1u, w, ST_TIMEOUT_TMEM_EMPTY)) break;
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!mbar_wait(&c.full[stage], phase, w, ST_TIMEOUT_PIPE_FULL)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(stage_base + stage * STAGE_BYTES);
+          const uint64_t adesc = make_smem_desc_sw128(sa);
+          const uint64_t bdesc = make_smem_desc_sw128(sa + A_STAGE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing 16 elements along K = 32 bytes = 2 descriptor units
+            umma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&c.empty[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        umma_commit(&c.tmem_full[acc]);
+      }
+      // all MMAs issued by this thread must retire before TMEM is freed
+      umma_commit(&c.drain);
+      WaitCtx wd = w;
+      int no_abort = 0;
+      wd.abort_flag = &no_abort;
+      mbar_wait(&c.drain, 0, wd, ST_TIMEOUT_DRAIN);
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue
+    constexpr int OUT_TILE = (EPI == B200_EPI_SILU_GATE) ? BN / 2 : BN;   // output cols per tile
+    constexpr int PASSES = OUT_TILE / STG_COLS;
+    const int q = warp & 3;                      // TMEM lane quarter this warp may read
+    const int row_in_tile = q * 32 + lane;
+    uint8_t* my_stg = staging + row_in_tile * STG_ROW_BYTES;
+    int cursor = 0, it = 0;
+    for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, ++it) {
+      int g, m, n;
+      if (!decode_tile(c, G, TN, gm, idx, cursor, g, m, n)) break;
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int rows_in_tile = min(BM, c.g_rows[g] - m * BM);
+      const int row0 = c.g_row_start[g] + m * BM;
+      bool valid = row_in_tile < rows_in_tile;
+
+      unsigned long long my_dst = 0;     // byte address of this thread's output row
+      float wgt = 1.0f;
+      int dst_rank = -1;
+      if constexpr (EPI == B200_EPI_COMBINE) {
+        if (valid) {
+          const uint2 meta = __ldcg(reinterpret_cast<const uint2*>(ca.row_meta) + row0 + row_in_tile);
+          dst_rank = static_cast<int>(meta.x >> 24);
+          const int slot = static_cast<int>(meta.x & 0xFFFFFFu);
+          wgt = __uint_as_float(meta.y);
+          if (dst_rank >= ca.world || slot >= ca.max_slots) {
+            report_status(w.status, ST_BAD_INDEX);
+            valid = false;
+            dst_rank = -1;
+          } else {
+            my_dst = ca.peer_out[dst_rank] +
+                     static_cast<unsigned long long>(slot) * ca.out_row_stride * 2ull;
+          }
+        }
+      } else {
+        my_dst = reinterpret_cast<unsigned long long>(ga.out) +
+                 static_cast<unsigned long long>(row0 + row_in_tile) * ga.ldo * 2ull;
+      }
+
+      // warp-uniform decision: the TMEM loads below need the whole warp
+      const bool got = mbar_wait(&c.tmem_full[acc], acc_phase, w, ST_TIMEOUT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after_sync();
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+
+#pragma unroll 1
+      for (int p = 0; p < PASSES; ++p) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int cc = p * STG_COLS + h * 32;
+          uint32_t v[32];
+          uint32_t packed[16];
+          if constexpr (EPI == B200_EPI_SILU_GATE) {
+            uint32_t u[32];
+            tmem_ld_32x32b_x32(t_acc + cc, v);             // gate block
+            tmem_ld_32x32b_x32(t_acc + BN / 2 + cc, u);    // up block
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const float a0 = silu_f(__uint_as_float(v[2 * i])) * __uint_as_float(u[2 * i]);
+              const float a1 = silu_f(__uint_as_float(v[2 * i + 1])) * __uint_as_float(u[2 * i + 1]);
+              packed[i] = pack_bf16x2(a0, a1);
+            }
+          } else {
+            tmem_ld_32x32b_x32(t_acc + cc, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              packed[i] = pack_bf16x2(__uint_as_float(v[2 * i]) * wgt,
+                                      __uint_as_float(v[2 * i + 1]) * wgt);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            *reinterpret_cast<uint4*>(my_stg + h * 64 + i * 16) =
+                make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
+          }
+        }
+        if (p == PASSES - 1) {
+          // every TMEM read of this accumulator is done: hand it back to the MMA warp
+          tc_fence_before_sync();
+          mbar_arrive(&c.tmem_empty[acc]);
+        }
+        __syncwarp();
+        // coalesced write-out: 8 lanes cover one 128-byte row segment, 4 rows per step
+        const int col0 = n * OUT_TILE + p * STG_COLS + (lane & 7) * 8;
+#pragma unroll
+        for (int rr = 0; rr < 8; ++rr) {
+          const int r = rr * 4 + (lane >> 3);
+          const unsigned long long dst = __shfl_sync(0xffffffffu, my_dst, r);
+          const int rvalid = __shfl_sync(0xffffffffu, valid ? 1 : 0, r);
+          if (rvalid && col0 < ga.n_out) {
+            const uint4 val = *reinterpret_cast<const uint4*>(
+                staging + (q * 32 + r) * STG_ROW_BYTES + (lane & 7) * 16);
+            st_16(reinterpret_cast<void*>(dst + static_cast<unsigned long long>(col0) * 2ull), val);
+          }
+        }
+        __syncwarp();
+      }
+
+      if constexpr (EPI == B200_EPI_COMBINE) {
+        // one arrival count per (row, n-tile), summed per destination rank
+        const unsigned grp = __match_any_sync(0xffffffffu, dst_rank);
+        if (dst_rank >= 0 && lane == (__ffs(grp) - 1)) {
+          fence_acq_rel_sys();
+          red_add_release_sys(reinterpret_cast<uint32_t*>(ca.peer_arrived[dst_rank]),
+                              static_cast<uint32_t>(__popc(grp)));
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ token senders
+    if constexpr (FUSED) {
+      const int stid = tid - 6 * 32;            // 0..127 inside the sender group
+      const int swarp = stid >> 5;
+      const int ET = da.world * da.e_local;
+      const int total_units = c.total_units;
+      const int k16 = ga.K / 8;                 // 16-byte chunks per token row
+      int bcur = 0;
+      // The loop bound is uniform over the four sender warps (they meet at a
+      // named barrier per unit), so it must not depend on the abort flag.
+      for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+        while (bcur < ET && u >= c.b_unit_start[bcur + 1]) ++bcur;
+        if (bcur >= ET) break;
+        const int j = u - c.b_unit_start[bcur];
+        const int rel0 = c.b_dst_rel0[bcur];
+        const int nrows = c.b_count[bcur];
+        const int tile = rel0 / BM + j;          // M-tile inside the destination expert
+        const int p_lo = max(0, tile * BM - rel0);
+        const int p_hi = min(nrows, (tile + 1) * BM - rel0);
+        const int dst = c.b_dst_rank[bcur];
+        const int send0 = c.b_send_start[bcur];
+        const int drow0 = c.b_dst_row[bcur];
+        uint8_t* recv = reinterpret_cast<uint8_t*>(da.peer_recv[dst]);
+        uint2* meta = reinterpret_cast<uint2*>(da.peer_meta[dst]);
+        for (int p = p_lo + swarp; p < p_hi; p += 4) {
+          const int flat = __ldg(da.send_order + send0 + p);
+          const int t = flat / da.topk;
+          const int drow = drow0 + p;
+          if (t < 0 || t >= da.num_tokens || drow >= da.cap_rows) {
+            if (lane == 0) report_status(w.status, ST_BAD_INDEX);
+            continue;
+          }
+          const uint4* src = reinterpret_cast<const uint4*>(da.x) + static_cast<size_t>(t) * k16;
+          uint4* out = reinterpret_cast<uint4*>(recv + static_cast<size_t>(drow) * ga.K * 2);
+          for (int i = lane; i < k16; i += 128) {
+            uint4 v0, v1, v2, v3;
+            const bool h1 = i + 32 < k16, h2 = i + 64 < k16, h3 = i + 96 < k16;
+            v0 = ld_nc_16(src + i);
+            if (h1) v1 = ld_nc_16(src + i + 32);
+            if (h2) v2 = ld_nc_16(src + i + 64);
+            if (h3) v3 = ld_nc_16(src + i + 96);
+            st_16(out + i, v0);
+            if (h1) st_16(out + i + 32, v1);
+            if (h2) st_16(out + i + 64, v2);
+            if (h3) st_16(out + i + 96, v3);
+          }
+          if (lane == 0) {
+            uint2 mv;
+            mv.x = (static_cast<uint32_t>(da.rank) << 24) | static_cast<uint32_t>(flat);
+            mv.y = __float_as_uint(__ldg(da.topk_weight + flat));
+            meta[drow] = mv;
+          }
+        }
+        // all four sender warps have stored their rows of this unit
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (stid == 0 && !da.drop_signal) {
+          fence_acq_rel_sys();
+          red_add_release_sys(reinterpret_cast<uint32_t*>(da.peer_ready[dst]) +
+                                  c.b_dst_mtile0[bcur] + tile,
+                              static_cast<uint32_t>(p_hi - p_lo));
+        }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+  }
+  return fn;
+}
+
+// Row-major bf16 matrix [rows, cols]; box = [box_rows, 64 columns]; 128-byte swizzle.
+static int make_tmap_bf16(CUtensorMap* tm, const void* base, long long rows, long long cols,
+                          int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return -1;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) != 0 || (cols * 2) % 16 != 0 || rows <= 0) return -2;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+template <int EPI, bool FUSED>
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const b200_gemm_args& ga,
+                          const b200_dispatch_args& da, const b200_combine_args& ca, int ctas,
+                          cudaStream_t stream) {
+  static bool configured = false;
+  auto kern = grouped_gemm_kernel<EPI, FUSED>;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  kern<<<ctas, FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, SMEM_BYTES, stream>>>(ta, tb, ga, da, ca);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace b200
+
+extern "C" {
+
+// Launches the grouped GEMM.  `a`/`a_rows` describe the packed activation
+// buffer (for the fused-dispatch build: this rank's receive buffer and its
+// capacity), `w` is [G*N, K].  Returns 0 or a negative (descriptor) / positive
+// (cudaError_t) error code.  Nothing is allocated.
+int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, int fused,
+                      const b200_gemm_args* ga, const b200_dispatch_args* da,
+                      const b200_combine_args* ca, int num_ctas, void* stream) {
+  using namespace b200;
+  if (ga == nullptr || ga->K % 8 != 0 || ga->N % 8 != 0 || ga->n_out % 8 != 0) return -10;
+  const int G = fused ? (da ? da->e_local : 0) : ga->num_groups;
+  if (G <= 0 || G > B200_MAX_GROUPS) return -11;
+  if (fused && (da == nullptr || da->world * da->e_local > B200_MAX_EXPERTS ||
+                da->world > B200_MAX_WORLD))
+    return -12;
+  if (epi == B200_EPI_COMBINE && ca == nullptr) return -13;
+  CUtensorMap ta, tb;
+  int r = make_tmap_bf16(&ta, a, a_rows, ga->K, BM);
+  if (r != 0) return r;
+  r = make_tmap_bf16(&tb, w, static_cast<long long>(G) * ga->N, ga->K, BN);
+  if (r != 0) return r - 10;
+  b200_dispatch_args dz;
+  b200_combine_args cz;
+  memset(&dz, 0, sizeof(dz));
+  memset(&cz, 0, sizeof(cz));
+  const b200_dispatch_args& d = da ? *da : dz;
+  const b200_combine_args& c = ca ? *ca : cz;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (num_ctas <= 0) return -14;
+  if (!fused) {
+    switch (epi) {
+      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, false>(ta, tb, *ga, d, c, num_ctas, st);
+      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, false>(ta, tb, *ga, d, c, num_ctas, st);
+      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, false>(ta, tb, *ga, d, c, num_ctas, st);
+    }
+  } else {
+    switch (epi) {
+      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, true>(ta, tb, *ga, d, c, num_ctas, st);
+      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, true>(ta, tb, *ga, d, c, num_ctas, st);
+    }
+  }
+  return -15;
+}
+
+int b200_gemm_smem_bytes() { return b200::SMEM_BYTES; }
+
+}  // extern "C"

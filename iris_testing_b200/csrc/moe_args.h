@@ -1,0 +1,67 @@
+// Plain-C argument blocks shared by the host launchers and the device kernels
+// of the MoE expert-parallel pipeline.  All pointers are device pointers in the
+// calling rank's address space; "peer_*" arrays hold, per rank, the address at
+// which that rank's copy of a symmetric buffer is mapped locally.
+#pragma once
+#include <stdint.h>
+
+#define B200_MAX_WORLD 8
+#define B200_MAX_GROUPS 128    // local experts per rank
+#define B200_MAX_EXPERTS 128   // experts in the whole EP group
+
+// Epilogue selectors of the grouped GEMM.
+#define B200_EPI_STORE 0       // out[row, n]            = acc
+#define B200_EPI_SILU_GATE 1   // out[row, n]            = silu(acc_gate) * acc_up
+#define B200_EPI_COMBINE 2     // peer_out[src][slot, n] = weight(row) * acc
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Routing / dispatch side of the fused "dispatch -> grouped GEMM" kernel.
+typedef struct {
+  int world;
+  int rank;
+  int e_local;
+  int topk;
+  int num_tokens;                 // T: tokens held by this rank
+  const void* x;                  // [T, K] bf16, this rank's tokens
+  const int* send_order;          // [T*topk] flat (t*topk+slot), sorted by (expert, t, slot)
+  const float* topk_weight;       // [T*topk]
+  const int* counts_all;          // [world(src)][world(dst)][e_local], written by peers
+  const uint32_t* counts_flag;    // [world], epoch stamped by each source rank
+  uint32_t epoch;                 // 1-based iteration stamp expected in counts_flag
+  int cap_rows;                   // receive capacity (rows) of every rank
+  int drop_signal;                // testing aid: do not signal tile arrival
+  unsigned long long peer_recv[B200_MAX_WORLD];   // bf16 [cap_rows, K]
+  unsigned long long peer_meta[B200_MAX_WORLD];   // uint2 [cap_rows]: {src<<24|slot, weight}
+  unsigned long long peer_ready[B200_MAX_WORLD];  // uint32 [cap_mtiles] rows landed per M-tile
+  int* group_rows_out;            // [e_local] rows per local expert (for the second GEMM)
+} b200_dispatch_args;
+
+// Combine side (epilogue of the second grouped GEMM).
+typedef struct {
+  int world;
+  const void* row_meta;           // uint2 [rows]: {src<<24|slot, weight}
+  long long out_row_stride;       // elements between slot rows (= model dim)
+  int max_slots;                  // T*topk of the largest rank (bounds check)
+  unsigned long long peer_out[B200_MAX_WORLD];      // bf16 [T*topk, D] slot buffer per rank
+  unsigned long long peer_arrived[B200_MAX_WORLD];  // uint32 arrival counter per rank
+} b200_combine_args;
+
+typedef struct {
+  int num_groups;                 // G
+  int N;                          // weight rows per group
+  int K;                          // reduction dim
+  int n_out;                      // output columns (N, or N/2 when gated)
+  int group_m;                    // M-tiles per scheduling chunk (L2 blocking)
+  const int* group_rows;          // [G] rows per group (compact layout); null when fused-in
+  void* out;                      // EPI 0/1 output base
+  long long ldo;                  // EPI 0/1 output row stride (elements)
+  int* status;                    // this rank's status word
+  unsigned long long wait_budget_ns;
+} b200_gemm_args;
+
+#ifdef __cplusplus
+}
+#endif
