@@ -1,0 +1,422 @@
+// Stand-alone (unfused) expert-parallel exchange kernels over symmetric peer
+// memory: the padded dispatch with the reference's buffer contract, its mirror
+// (padded return), token shuffle / unshuffle, the slot reduction that ends the
+// fused combine, the SiLU gate and the cross-rank barrier.
+//
+// Counterparts in the reference project: kernels.py:21-66 (counts exchange) and
+// kernels.py:69-146 (token exchange) become padded_dispatch_kernel; the shuffle
+// design of kernels.py:150-205 / layers/token_shuffle.py:31-56 becomes
+// shuffle_kernel; the host barrier of benchmark.py:194 becomes barrier_kernel.
+// The return path, unshuffle, slot reduction and activation have no reference
+// counterpart.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "moe_args.h"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+struct PeerTable {
+  unsigned long long p[B200_MAX_WORLD];
+};
+
+// ---------------------------------------------------------------------------
+// Padded dispatch.  Layouts (identical to the reference's data contract):
+//   send_payload [sum_send, H]  rows ordered by destination, then local expert
+//   send_counts  [world, e_local]
+//   dst_offsets  [world]        first payload row of each destination
+//   pca          [e_local, world]  on the destination: pca[e, src] = rows sent
+//   token_buf    [e_local, world, CAP, H] on the destination
+//   counts_ready [1], token_sync [e_local]: arrival counters on the destination
+// Grid: (m_tiles, e_local, world).  A block copies up to `block_m` rows of one
+// (dst, expert) cell and then adds 1 to token_sync[expert] on dst -- the
+// per-tile completion rule (receiver expects sum_src ceil(pca[e,src]/block_m)).
+// Blocks with blockIdx.x == 0 and blockIdx.y == 0 also deliver the counts.
+// ---------------------------------------------------------------------------
+__global__ void padded_dispatch_kernel(const uint4* __restrict__ payload,
+                                       const int* __restrict__ send_counts,
+                                       const int* __restrict__ dst_offsets, PeerTable peer_pca,
+                                       PeerTable peer_token_buf, PeerTable peer_counts_ready,
+                                       PeerTable peer_token_sync, int rank, int world, int e_local,
+                                       int cap, int row16, int block_m, int* status) {
+  const int dst = blockIdx.z, e = blockIdx.y, mt = blockIdx.x;
+  if (mt == 0 && e == 0) {
+    int* pca = reinterpret_cast<int*>(peer_pca.p[dst]);
+    for (int e2 = threadIdx.x; e2 < e_local; e2 += blockDim.x)
+      pca[e2 * world + rank] = send_counts[dst * e_local + e2];
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_acq_rel_sys();
+      red_add_release_sys(reinterpret_cast<uint32_t*>(peer_counts_ready.p[dst]), 1u);
+    }
+  }
+  const int n_true = send_counts[dst * e_local + e];
+  if (n_true > cap && mt == 0 && threadIdx.x == 0) report_status(status, ST_OVERFLOW);
+  const int n = min(n_true, cap);            // rows beyond the cell's capacity are dropped
+  const int m0 = mt * block_m;
+  if (m0 >= n) return;                       // empty tile: nothing to send, nothing to signal
+  int eoff = 0;
+  for (int e2 = 0; e2 < e; ++e2) eoff += send_counts[dst * e_local + e2];
+  const size_t src_row0 = static_cast<size_t>(dst_offsets[dst]) + eoff + m0;
+  uint4* tb = reinterpret_cast<uint4*>(peer_token_buf.p[dst]);
+  const size_t dst_row0 = (static_cast<size_t>(e) * world + rank) * cap + m0;
+  const int rows = min(block_m, n - m0);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int r = warp; r < rows; r += nwarps) {
+    const uint4* s = payload + (src_row0 + r) * row16;
+    uint4* d = tb + (dst_row0 + r) * row16;
+    for (int i = lane; i < row16; i += 32) st_16(d + i, ld_nc_16(s + i));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
+    red_add_release_sys(reinterpret_cast<uint32_t*>(peer_token_sync.p[dst]) + e, 1u);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Padded return (the mirror): the expert rank sends the processed rows of
+// cell (e, src) back to rank src, where they land in
+//   ret_buf [world(expert rank), e_local, CAP, H]
+// so that row (dst, e, m) of ret_buf answers payload row
+// dst_offsets[dst] + expert_offs[dst, e] + m.  ret_sync[world] on the source
+// counts tiles per expert rank.
+// ---------------------------------------------------------------------------
+__global__ void padded_return_kernel(const uint4* __restrict__ out_buf, const int* __restrict__ pca,
+                                     PeerTable peer_ret_buf, PeerTable peer_ret_sync, int rank,
+                                     int world, int e_local, int cap, int row16, int block_m) {
+  const int src = blockIdx.z, e = blockIdx.y, mt = blockIdx.x;
+  const int n = min(pca[e * world + src], cap);
+  const int m0 = mt * block_m;
+  if (m0 >= n) return;
+  const int rows = min(block_m, n - m0);
+  const size_t in_row0 = (static_cast<size_t>(e) * world + src) * cap + m0;
+  uint4* rb = reinterpret_cast<uint4*>(peer_ret_buf.p[src]);
+  const size_t out_row0 = (static_cast<size_t>(rank) * e_local + e) * cap + m0;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  for (int r = warp; r < rows; r += nwarps) {
+    const uint4* s = out_buf + (in_row0 + r) * row16;
+    uint4* d = rb + (out_row0 + r) * row16;
+    for (int i = lane; i < row16; i += 32) st_16(d + i, ld_16(s + i));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    fence_acq_rel_sys();
+    red_add_release_sys(reinterpret_cast<uint32_t*>(peer_ret_sync.p[src]) + rank, 1u);
+  }
+}
+
+// y[t, :] = sum_slot w[t, slot] * ret_buf[cell(t, slot), :] -- the top-k
+// weighted sum on the source rank.  dst_slot[t*k+slot] is the payload row of
+// that copy; bucket_start / send_counts locate its (dst, e, m) cell.
+// Waits (bounded) until every expert rank has returned its tiles.
+__global__ void weighted_gather_kernel(const __nv_bfloat16* __restrict__ ret_buf,
+                                       const int* __restrict__ dst_slot,
+                                       const int* __restrict__ topk_idx,
+                                       const int* __restrict__ bucket_start,
+                                       const float* __restrict__ topk_w, const uint32_t* ret_sync,
+                                       const int* __restrict__ send_counts, int T, int topk, int world,
+                                       int e_local, int cap, int H, int block_m,
+                                       __nv_bfloat16* __restrict__ y, int* status,
+                                       unsigned long long budget_ns) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    uint32_t expect = 0;
+    for (int e = 0; e < e_local; ++e)
+      expect += (min(send_counts[threadIdx.x * e_local + e], cap) + block_m - 1) / block_m;
+    WaitCtx w; w.abort_flag = &s_abort; w.status = status; w.budget_ns = budget_ns;
+    wait_flag_geq(ret_sync + threadIdx.x, expect, w, ST_TIMEOUT_COMBINE);
+  }
+  __syncthreads();
+  if (s_abort) return;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int t = warp; t < T; t += nwarps) {
+    for (int c0 = lane * 8; c0 < H; c0 += 256) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int s = 0; s < topk; ++s) {
+        const int flat = t * topk + s;
+        const int ge = topk_idx[flat];
+        const int m = dst_slot[flat] - bucket_start[ge];
+        if (m >= cap) continue;   // dropped by capacity
+        const size_t row = static_cast<size_t>(ge) * cap + m;   // [dst, e] flattens to ge
+        const uint4 v = ld_16(reinterpret_cast<const uint4*>(ret_buf + row * H + c0));
+        const float wv = topk_w[flat];
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(h2[j]);
+          acc[2 * j] += wv * f.x;
+          acc[2 * j + 1] += wv * f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+      o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+      *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * H + c0) = o;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Token shuffle: drop the padding.  packed[off(e,src) + m, :] = token_buf[e, src, m, :]
+// for m < pca[e, src], off = exclusive cumsum of pca in (e, src) order.  With
+// `wait` set, first waits (bounded) for counts_ready >= world and for
+// token_sync[e] >= sum_src ceil(pca[e,src]/block_m).  `inverse` scatters back.
+// ---------------------------------------------------------------------------
+__global__ void shuffle_kernel(uint4* token_buf, uint4* packed, const int* pca,
+                               const uint32_t* counts_ready, const uint32_t* token_sync, int world,
+                               int e_local, int cap, int row16, int block_m, int wait, int inverse,
+                               int* group_rows, int* status, unsigned long long budget_ns) {
+  __shared__ int s_off[B200_MAX_EXPERTS + 1];   // e_local * world cells
+  __shared__ int s_abort;
+  const int cells = e_local * world;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  WaitCtx w; w.abort_flag = &s_abort; w.status = status; w.budget_ns = budget_ns;
+  if (wait) {
+    if (threadIdx.x == 0) wait_flag_geq(counts_ready, static_cast<uint32_t>(world), w, ST_TIMEOUT_COUNTS);
+    __syncthreads();
+    if (threadIdx.x < e_local && !s_abort) {
+      uint32_t expect = 0;
+      for (int s = 0; s < world; ++s)
+        expect += (min(__ldcg(pca + threadIdx.x * world + s), cap) + block_m - 1) / block_m;
+      wait_flag_geq(token_sync + threadIdx.x, expect, w, ST_TIMEOUT_TILE_READY);
+    }
+    __syncthreads();
+    if (s_abort) return;
+  }
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int c = 0; c < cells; ++c) { s_off[c] = acc; acc += min(__ldcg(pca + c), cap); }
+    s_off[cells] = acc;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0 && group_rows != nullptr)
+    for (int e = threadIdx.x; e < e_local; e += blockDim.x)
+      group_rows[e] = s_off[(e + 1) * world] - s_off[e * world];
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const int total = s_off[cells];
+  int cell = 0;
+  for (int r = warp; r < total; r += nwarps) {
+    while (r >= s_off[cell + 1]) ++cell;
+    const int m = r - s_off[cell];
+    uint4* pad = token_buf + (static_cast<size_t>(cell) * cap + m) * row16;
+    uint4* pk = packed + static_cast<size_t>(r) * row16;
+    if (!inverse) for (int i = lane; i < row16; i += 32) pk[i] = ld_16(pad + i);
+    else          for (int i = lane; i < row16; i += 32) pad[i] = ld_16(pk + i);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Slot reduction ending the fused combine: wait (bounded) until `expected`
+// (row, n-tile) units have landed in out_slots, then y[t] = sum_slot
+// out_slots[t*k+slot] in slot order (deterministic).  The last block to finish
+// re-arms the per-iteration state (arrival counter, this parity's tile-ready
+// counters) and tells every peer that this rank has retired the iteration.
+// ---------------------------------------------------------------------------
+struct RetireArgs {
+  int world, rank;
+  uint32_t iter_done_value;          // iterations retired after this one
+  unsigned long long peer_iter_done[B200_MAX_WORLD];   // uint32 [world] on each rank
+  uint32_t* ready_counters;          // this parity's tile-ready counters (local)
+  int num_ready;
+  unsigned int* ticket;              // local scratch counter (zero between launches)
+};
+
+__global__ void slot_reduce_kernel(const __nv_bfloat16* out_slots, uint32_t* arrived,
+                                   uint32_t expected, int T, int topk, int H,
+                                   __nv_bfloat16* __restrict__ y, RetireArgs ra, int* status,
+                                   unsigned long long budget_ns) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    WaitCtx w; w.abort_flag = &s_abort; w.status = status; w.budget_ns = budget_ns;
+    wait_flag_geq(arrived, expected, w, ST_TIMEOUT_COMBINE);
+  }
+  __syncthreads();
+  if (!s_abort) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    for (int t = warp; t < T; t += nwarps) {
+      for (int c0 = lane * 8; c0 < H; c0 += 256) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int s = 0; s < topk; ++s) {
+          const uint4 v = ld_16(reinterpret_cast<const uint4*>(
+              out_slots + (static_cast<size_t>(t) * topk + s) * H + c0));
+          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(h2[j]);
+            acc[2 * j] += f.x;
+            acc[2 * j + 1] += f.y;
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+        *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * H + c0) = o;
+      }
+    }
+  }
+  // retire the iteration (last block only)
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = (atomicAdd(ra.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (s_last) {
+    for (int i = threadIdx.x; i < ra.num_ready; i += blockDim.x) ra.ready_counters[i] = 0u;
+    if (threadIdx.x == 0) { *arrived = 0u; *ra.ticket = 0u; }
+    __syncthreads();
+    if (threadIdx.x < ra.world) {
+      fence_acq_rel_sys();
+      st_release_sys(reinterpret_cast<uint32_t*>(ra.peer_iter_done[threadIdx.x]) + ra.rank,
+                     ra.iter_done_value);
+    }
+  }
+}
+
+// h[r, j] = silu(gate[r, j]) * up[r, j]
+__global__ void silu_gate_kernel(const __nv_bfloat162* __restrict__ gate,
+                                 const __nv_bfloat162* __restrict__ up,
+                                 __nv_bfloat162* __restrict__ out, size_t n2) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n2;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float2 g = __bfloat1622float2(gate[i]);
+    const float2 u = __bfloat1622float2(up[i]);
+    out[i] = __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+  }
+}
+
+// Cross-rank barrier: publish `epoch` into slot [rank] of every peer's flag
+// array, then wait (bounded) until all local slots have reached it.
+__global__ void barrier_kernel(PeerTable peer_flags, uint32_t* local_flags, int rank, int world,
+                               uint32_t epoch, int* status, unsigned long long budget_ns) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  if (threadIdx.x < world) {
+    fence_acq_rel_sys();
+    st_release_sys(reinterpret_cast<uint32_t*>(peer_flags.p[threadIdx.x]) + rank, epoch);
+    WaitCtx w; w.abort_flag = &s_abort; w.status = status; w.budget_ns = budget_ns;
+    wait_flag_geq(local_flags + threadIdx.x, epoch, w, ST_TIMEOUT_BARRIER);
+  }
+}
+
+}  // namespace b200
+
+
+extern "C" {
+
+using b200::PeerTable;
+
+static PeerTable make_table(const unsigned long long* p, int world) {
+  PeerTable t;
+  memset(&t, 0, sizeof(t));
+  for (int i = 0; i < world && i < B200_MAX_WORLD; ++i) t.p[i] = p[i];
+  return t;
+}
+
+int b200_padded_dispatch(const void* payload, const int* send_counts, const int* dst_offsets,
+                         const unsigned long long* peer_pca, const unsigned long long* peer_token_buf,
+                         const unsigned long long* peer_counts_ready,
+                         const unsigned long long* peer_token_sync, int rank, int world, int e_local,
+                         int cap, int hidden_dim, int block_m, int* status, void* stream) {
+  if (hidden_dim % 8 != 0 || world > B200_MAX_WORLD || world * e_local > B200_MAX_EXPERTS ||
+      block_m < 1 || cap < 1)
+    return -1;
+  dim3 grid((cap + block_m - 1) / block_m, e_local, world);
+  b200::padded_dispatch_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(payload), send_counts, dst_offsets, make_table(peer_pca, world),
+      make_table(peer_token_buf, world), make_table(peer_counts_ready, world),
+      make_table(peer_token_sync, world), rank, world, e_local, cap, hidden_dim / 8, block_m, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int b200_padded_return(const void* out_buf, const int* pca, const unsigned long long* peer_ret_buf,
+                       const unsigned long long* peer_ret_sync, int rank, int world, int e_local,
+                       int cap, int hidden_dim, int block_m, void* stream) {
+  if (hidden_dim % 8 != 0 || world > B200_MAX_WORLD || block_m < 1 || cap < 1) return -1;
+  dim3 grid((cap + block_m - 1) / block_m, e_local, world);
+  b200::padded_return_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(out_buf), pca, make_table(peer_ret_buf, world),
+      make_table(peer_ret_sync, world), rank, world, e_local, cap, hidden_dim / 8, block_m);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int b200_weighted_gather(const void* ret_buf, const int* dst_slot, const int* topk_idx,
+                         const int* bucket_start, const float* topk_w, const void* ret_sync,
+                         const int* send_counts, int T, int topk, int world, int e_local, int cap,
+                         int hidden_dim, int block_m, void* y, int* status,
+                         unsigned long long budget_ns, void* stream) {
+  if (hidden_dim % 8 != 0 || world > 32) return -1;
+  int blocks = (T + 7) / 8;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  b200::weighted_gather_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(ret_buf), dst_slot, topk_idx, bucket_start, topk_w,
+      static_cast<const uint32_t*>(ret_sync), send_counts, T, topk, world, e_local, cap, hidden_dim,
+      block_m, static_cast<__nv_bfloat16*>(y), status, budget_ns);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int b200_shuffle(void* token_buf, void* packed, const int* pca, const void* counts_ready,
+                 const void* token_sync, int world, int e_local, int cap, int hidden_dim, int block_m,
+                 int wait, int inverse, int* group_rows, int* status, unsigned long long budget_ns,
+                 void* stream) {
+  if (hidden_dim % 8 != 0 || world * e_local > B200_MAX_EXPERTS) return -1;
+  b200::shuffle_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<uint4*>(token_buf), static_cast<uint4*>(packed), pca,
+      static_cast<const uint32_t*>(counts_ready), static_cast<const uint32_t*>(token_sync), world,
+      e_local, cap, hidden_dim / 8, block_m, wait, inverse, group_rows, status, budget_ns);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int b200_slot_reduce(const void* out_slots, void* arrived, unsigned int expected, int T, int topk,
+                     int hidden_dim, void* y, const b200::RetireArgs* ra, int* status,
+                     unsigned long long budget_ns, void* stream) {
+  if (hidden_dim % 8 != 0 || ra == nullptr) return -1;
+  int blocks = (T + 7) / 8;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  b200::slot_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(out_slots), static_cast<uint32_t*>(arrived), expected, T,
+      topk, hidden_dim, static_cast<__nv_bfloat16*>(y), *ra, status, budget_ns);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int b200_silu_gate(const void* gate, const void* up, void* out, long long n, void* stream) {
+  if (n % 2 != 0) return -1;
+  if (n == 0) return 0;
+  long long n2 = n / 2;
+  long long blocks = (n2 + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  b200::silu_gate_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat162*>(gate), static_cast<const __nv_bfloat162*>(up),
+      static_cast<__nv_bfloat162*>(out), static_cast<size_t>(n2));
+  return static_cast<int>(cudaGetLastError());
+}
+
+int b200_barrier(const unsigned long long* peer_flags, void* local_flags, int rank, int world,
+                 unsigned int epoch, int* status, unsigned long long budget_ns, void* stream) {
+  if (world > B200_MAX_WORLD) return -1;
+  b200::barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      make_table(peer_flags, world), static_cast<uint32_t*>(local_flags), rank, world, epoch, status,
+      budget_ns);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

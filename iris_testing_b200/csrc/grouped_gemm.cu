@@ -616,6 +616,7 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
     switch (epi) {
       case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, true>(ta, tb, *ga, d, c, num_ctas, st);
       case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, true>(ta, tb, *ga, d, c, num_ctas, st);
+      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, true>(ta, tb, *ga, d, c, num_ctas, st);
     }
   }
   return -15;

@@ -1,0 +1,276 @@
+// Routing kernels: softmax -> top-k router, and the dispatch plan (per-expert
+// histogram, stable rank of every routed copy inside its expert bucket, packed
+// send order, and the push of this rank's counts to every peer).
+//
+// Counterparts in the reference project: the router math of utils.py:201-202,
+// the Python bucket/pack loop of utils.py:204-246, the offset builders of
+// utils.py:20-31 and benchmark.py:44-49, and the counts exchange kernel of
+// kernels.py:21-66 (folded into plan_finalize_kernel).
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+#include <string.h>
+
+#include "moe_args.h"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+
+constexpr int ROUTER_MAX_K = 8;
+
+// Keeps the largest (value, index) pairs seen so far in descending order.
+struct TopK {
+  float v[ROUTER_MAX_K];
+  int i[ROUTER_MAX_K];
+  __device__ __forceinline__ void init() {
+#pragma unroll
+    for (int j = 0; j < ROUTER_MAX_K; ++j) { v[j] = -INFINITY; i[j] = -1; }
+  }
+  // Candidates must arrive in increasing index order: a strict comparison then
+  // keeps the lower index ahead on ties.
+  __device__ __forceinline__ void push(float x, int idx) {
+    float cv = x;
+    int ci = idx;
+#pragma unroll
+    for (int j = 0; j < ROUTER_MAX_K; ++j) {
+      if (cv > v[j]) {
+        const float tv = v[j]; const int ti = i[j];
+        v[j] = cv; i[j] = ci;
+        cv = tv; ci = ti;
+      }
+    }
+  }
+};
+
+// Generic CUDA-core router: one warp per token.  logits = x[t,:] . Wr[:, e] (+ bias[e]);
+// probabilities = softmax over experts; outputs the top-k (index, probability).
+// Wr is [D, E] row-major as in the reference.  Used for shapes the tensor-core
+// router cannot take; O(T*D*E) loads from L2.
+__global__ void router_topk_simple_kernel(const __nv_bfloat16* __restrict__ x,
+                                          const __nv_bfloat16* __restrict__ wr,
+                                          const float* __restrict__ bias, int T, int D, int E, int k,
+                                          int renorm, int* __restrict__ topk_idx,
+                                          float* __restrict__ topk_w, float* __restrict__ logits_out) {
+  extern __shared__ float sm_logits[];   // [warps][E]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  float* lg = sm_logits + warp * E;
+  for (int t = blockIdx.x * warps + warp; t < T; t += gridDim.x * warps) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(t) * D;
+    for (int e0 = 0; e0 < E; e0 += 8) {
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int d = lane; d < D; d += 32) {
+        const float xv = __bfloat162float(xr[d]);
+        const __nv_bfloat16* wrow = wr + static_cast<size_t>(d) * E + e0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (e0 + j < E) acc[j] += xv * __bfloat162float(wrow[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float a = acc[j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0 && e0 + j < E) lg[e0 + j] = a + (bias ? bias[e0 + j] : 0.f);
+      }
+    }
+    __syncwarp();
+    // softmax statistics
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += __expf(lg[e] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (logits_out) for (int e = lane; e < E; e += 32) logits_out[static_cast<size_t>(t) * E + e] = lg[e];
+    // top-k: lane-local candidates, then a k-round warp argmax merge
+    TopK tk; tk.init();
+    for (int e = lane; e < E; e += 32) tk.push(lg[e], e);
+    float wsum = 0.f;
+    float my_w = 0.f; int my_i = 0;
+    for (int r = 0; r < k; ++r) {
+      float bv = tk.v[0]; int bi = tk.i[0] < 0 ? 0x7fffffff : tk.i[0];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (tk.i[0] == bi) {   // the winning lane pops its head
+#pragma unroll
+        for (int j = 0; j < ROUTER_MAX_K - 1; ++j) { tk.v[j] = tk.v[j + 1]; tk.i[j] = tk.i[j + 1]; }
+        tk.v[ROUTER_MAX_K - 1] = -INFINITY; tk.i[ROUTER_MAX_K - 1] = -1;
+      }
+      const float p = __expf(bv - mx) / sum;
+      wsum += p;
+      if (lane == r) { my_w = p; my_i = bi; }
+    }
+    if (lane < k) {
+      topk_idx[static_cast<size_t>(t) * k + lane] = my_i;
+      topk_w[static_cast<size_t>(t) * k + lane] = renorm ? my_w / wsum : my_w;
+    }
+    __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Plan, step 1: one CTA per expert walks the flat (token, slot) list in order
+// and gives every copy routed to that expert its stable rank in the bucket.
+// ---------------------------------------------------------------------------
+__global__ void plan_rank_kernel(const int* __restrict__ topk_idx, int n_flat, int num_experts,
+                                 int* __restrict__ rank_in_bucket, int* __restrict__ counts) {
+  __shared__ int warp_cnt[32];
+  __shared__ int carry;
+  const int e = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  if (threadIdx.x == 0) carry = 0;
+  __syncthreads();
+  for (int base = 0; base < n_flat; base += blockDim.x) {
+    const int i = base + threadIdx.x;
+    const bool hit = (i < n_flat) && (topk_idx[i] == e);
+    const unsigned b = __ballot_sync(0xffffffffu, hit);
+    if (lane == 0) warp_cnt[warp] = __popc(b);
+    __syncthreads();
+    int before = carry;
+    for (int w2 = 0; w2 < warp; ++w2) before += warp_cnt[w2];
+    if (hit) rank_in_bucket[i] = before + __popc(b & ((1u << lane) - 1u));
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int tot = 0;
+      for (int w2 = 0; w2 < nwarps; ++w2) tot += warp_cnt[w2];
+      carry += tot;
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) counts[e] = carry;
+  (void)num_experts;
+}
+
+// ---------------------------------------------------------------------------
+// Plan, step 2: bucket offsets (exclusive scan over experts), the packed send
+// order, and -- when `peer_counts` is given -- the push of this rank's counts
+// row to every rank followed by an epoch-stamped flag.  Before touching a
+// peer's tables the kernel checks that the peer has retired the iteration that
+// last used the same parity slot.
+// ---------------------------------------------------------------------------
+struct PlanPushArgs {
+  int world, rank;
+  uint32_t epoch;                 // stamp to publish (iteration + 1)
+  uint32_t need_iter_done;        // every peer's iter_done must be >= this
+  const uint32_t* iter_done;      // [world] local: iterations retired by each peer
+  unsigned long long peer_counts[B200_MAX_WORLD];  // int [world][E_total] table on each rank
+  unsigned long long peer_flags[B200_MAX_WORLD];   // uint32 [world] flags on each rank
+  int* status;
+  unsigned long long wait_budget_ns;
+};
+
+__global__ void plan_finalize_kernel(const int* __restrict__ topk_idx,
+                                     const int* __restrict__ rank_in_bucket,
+                                     const int* __restrict__ counts, int n_flat, int num_experts,
+                                     int* __restrict__ bucket_start, int* __restrict__ send_order,
+                                     int* __restrict__ dst_slot, PlanPushArgs push, int do_push) {
+  __shared__ int s_start[B200_MAX_EXPERTS + 1];
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int e = 0; e < num_experts; ++e) { s_start[e] = acc; acc += counts[e]; }
+    s_start[num_experts] = acc;
+    s_abort = 0;
+  }
+  __syncthreads();
+  if (blockIdx.x == 0) {
+    for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) bucket_start[e] = s_start[e];
+    if (do_push) {
+      WaitCtx w; w.abort_flag = &s_abort; w.status = push.status; w.budget_ns = push.wait_budget_ns;
+      if (threadIdx.x < push.world)
+        wait_flag_geq(push.iter_done + threadIdx.x, push.need_iter_done, w, ST_TIMEOUT_ITER);
+      __syncthreads();
+      for (int p = 0; p < push.world; ++p) {
+        int* dst = reinterpret_cast<int*>(push.peer_counts[p]) + push.rank * num_experts;
+        for (int e = threadIdx.x; e < num_experts; e += blockDim.x) dst[e] = counts[e];
+      }
+      __syncthreads();
+      if (threadIdx.x < push.world) {
+        fence_acq_rel_sys();
+        st_release_sys(reinterpret_cast<uint32_t*>(push.peer_flags[threadIdx.x]) + push.rank,
+                       push.epoch);
+      }
+    }
+  }
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_flat; i += gridDim.x * blockDim.x) {
+    const int e = topk_idx[i];
+    if (e < 0 || e >= num_experts) continue;
+    const int pos = s_start[e] + rank_in_bucket[i];
+    send_order[pos] = i;
+    if (dst_slot) dst_slot[i] = pos;
+  }
+}
+
+// Gathers the packed send payload: payload[j, :] = x[send_order[j] / topk, :].
+__global__ void pack_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ send_order,
+                                 int n_flat, int topk, int row16, uint4* __restrict__ payload) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int j = warp; j < n_flat; j += nwarps) {
+    const int t = send_order[j] / topk;
+    const uint4* src = x + static_cast<size_t>(t) * row16;
+    uint4* dst = payload + static_cast<size_t>(j) * row16;
+    for (int i = lane; i < row16; i += 32) dst[i] = ld_nc_16(src + i);
+  }
+}
+
+}  // namespace b200
+
+extern "C" {
+
+int b200_router_topk_simple(const void* x, const void* wr, const float* bias, int T, int D, int E,
+                            int k, int renorm, int* topk_idx, float* topk_w, float* logits_out,
+                            void* stream) {
+  if (k < 1 || k > b200::ROUTER_MAX_K || k > E || E > 1024) return -1;
+  if (T == 0) return 0;
+  const int warps = 4;
+  const int blocks = (T + warps - 1) / warps;
+  b200::router_topk_simple_kernel<<<blocks < 65535 * 8 ? blocks : 65535 * 8, warps * 32,
+                                    warps * E * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(wr), bias, T, D, E, k,
+      renorm, topk_idx, topk_w, logits_out);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// topk_idx [n_flat] -> rank_in_bucket [n_flat], counts [E], bucket_start [E+1],
+// send_order [n_flat], dst_slot [n_flat] (optional).  `push` may be null.
+int b200_plan(const int* topk_idx, int n_flat, int num_experts, int* rank_in_bucket, int* counts,
+              int* bucket_start, int* send_order, int* dst_slot, const b200::PlanPushArgs* push,
+              void* stream) {
+  if (num_experts < 1 || num_experts > B200_MAX_EXPERTS) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  b200::plan_rank_kernel<<<num_experts, 1024, 0, st>>>(topk_idx, n_flat, num_experts, rank_in_bucket,
+                                                       counts);
+  b200::PlanPushArgs pz;
+  memset(&pz, 0, sizeof(pz));
+  int blocks = (n_flat + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 1184) blocks = 1184;
+  b200::plan_finalize_kernel<<<blocks, 256, 0, st>>>(topk_idx, rank_in_bucket, counts, n_flat,
+                                                     num_experts, bucket_start, send_order, dst_slot,
+                                                     push ? *push : pz, push ? 1 : 0);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int b200_pack_rows(const void* x, const int* send_order, int n_flat, int topk, int hidden_dim,
+                   void* payload, void* stream) {
+  if (hidden_dim % 8 != 0) return -1;
+  if (n_flat == 0) return 0;
+  int blocks = (n_flat + 7) / 8;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  b200::pack_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(x), send_order, n_flat, topk, hidden_dim / 8,
+      static_cast<uint4*>(payload));
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,315 @@
+"""``MoELayer``: one expert-parallel Mixture-of-Experts block.
+
+Forward pass on B200 (five launches, no host synchronisation):
+
+1. router          softmax -> top-k (indices + weights)
+2. plan            per-expert counts, stable bucket ranks, send order; pushes this
+                   rank's counts to every peer
+3. dispatch+GEMM1  ONE kernel: sender warps store routed token rows into the owning
+                   rank's receive buffer over NVLink and signal per M-tile, while the
+                   tcgen05 grouped GEMM of the same kernel consumes tiles as they land
+                   (SiLU-gate epilogue -> hidden activation, local HBM)
+4. GEMM2+combine   ONE kernel: second grouped GEMM whose epilogue scales each row by
+                   its top-k weight and stores it straight into the source rank's slot
+                   buffer, counting arrivals there
+5. slot reduce     waits for the arrivals, sums the k slots per token, retires the
+                   iteration (re-arms counters, tells peers the parity slot is free)
+
+The reference project wires none of this together (its intended forward pass is
+reconstructed from layers/all_to_all.py, layers/token_shuffle.py, layers/expert.py);
+router math follows utils.py:201-202 and the expert->rank map utils.py:216-218.
+
+On CPU tensors the layer runs the same math through PyTorch (and gloo when a
+process group is up), which is what the plumbing tests use.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import _native as nv
+from ..config import MoEConfig
+from ..ops import cpu_ref
+from ..ops._common import declare, ptr, stream_ptr
+from ..ops.expert import sm_count
+from ..ops.plan import Plan, PlanPushArgs, make_plan
+from ..ops.router import router_topk
+from ..utils import gen
+
+BM = 128          # rows per GEMM tile
+BN = 256          # weight rows per GEMM tile
+
+
+class RetireArgs(C.Structure):
+    _fields_ = [
+        ("world", C.c_int), ("rank", C.c_int),
+        ("iter_done_value", C.c_uint32),
+        ("peer_iter_done", C.c_ulonglong * nv.MAX_WORLD),
+        ("ready_counters", C.c_void_p),
+        ("num_ready", C.c_int),
+        ("ticket", C.c_void_p),
+    ]
+
+
+def heap_bytes_needed(cfg: MoEConfig, max_tokens: int, cap_rows: Optional[int] = None) -> int:
+    """Symmetric-heap bytes one ``MoELayer`` of this shape allocates (plus slack)."""
+    W, k, D = cfg.world_size, cfg.topk, cfg.hidden_dim
+    cap = cap_rows if cap_rows is not None else default_cap_rows(cfg, max_tokens)
+    mt = cap // BM + cfg.e_local + 1
+    total = 2 * cap * D * 2 + 2 * cap * 8 + 2 * mt * 4 + 2 * W * cfg.num_experts * 4
+    total += max_tokens * k * cfg.out_dim * 2
+    return total + (1 << 20)
+
+
+def default_cap_rows(cfg: MoEConfig, max_tokens: int) -> int:
+    worst = cfg.world_size * max_tokens * cfg.topk
+    if cfg.capacity_factor is None:
+        rows = worst
+    else:
+        rows = min(worst, int(cfg.capacity_factor * max_tokens * cfg.topk) + cfg.e_local * BM)
+    return (rows + BM - 1) // BM * BM
+
+
+class MoELayer(nn.Module):
+    """Expert-parallel MoE block: ``y = sum_k w_k * expert_k(x)``.
+
+    Parameters live in kernel-friendly ("K-major") layouts:
+
+    * ``router``  [D, E]                      (reference layout, utils.py:156-173)
+    * ``w13``     [e_local, 2F, D]  gated: blocks of 128 gate rows / 128 up rows
+                  [e_local, N, D]   single Linear (``cfg.gated == False``)
+    * ``w2``      [e_local, D, F]   gated only
+
+    ``load_reference_weights`` / ``reference_weights`` convert from / to the
+    ``x @ W`` layouts ([e, D, F], [e, D, F], [e, F, D]).
+    """
+
+    def __init__(self, cfg: MoEConfig, max_tokens: int, heap=None, device=None, seed: int = 0,
+                 rank: Optional[int] = None, router_std: Optional[float] = None,
+                 cap_rows: Optional[int] = None) -> None:
+        super().__init__()
+        self.cfg = cfg
+        self.max_tokens = int(max_tokens)
+        self.heap = heap
+        if rank is None:
+            rank = heap.rank if heap is not None else (
+                dist.get_rank() if dist.is_available() and dist.is_initialized() else 0)
+        self.rank = rank
+        device = torch.device(device) if device is not None else (
+            heap.device if heap is not None else torch.device("cpu"))
+        D, F, EL = cfg.hidden_dim, cfg.ffn_dim, cfg.e_local
+        self.router = nn.Parameter(gen.gen_router(D, cfg.num_experts, cfg.dtype, device, seed,
+                                                  std=router_std), requires_grad=False)
+        self.router_bias: Optional[torch.Tensor] = None
+        if cfg.gated:
+            if F % 128 != 0:
+                raise ValueError("gated experts need ffn_dim to be a multiple of 128")
+            w1, w3, w2 = gen.gen_gated_expert_weights(EL, D, F, cfg.dtype, device, seed, rank)
+            self.w13 = nn.Parameter(cpu_ref.interleave_gate_up(w1, w3), requires_grad=False)
+            self.w2 = nn.Parameter(w2.transpose(1, 2).contiguous(), requires_grad=False)
+        else:
+            w = gen.gen_local_weights(EL, D, cfg.out_dim, cfg.dtype, device, seed, rank)
+            self.w13 = nn.Parameter(w.transpose(1, 2).contiguous(), requires_grad=False)
+            self.w2 = None
+        self._iteration = 0
+        self._engine_ready = False
+        self._cap_rows = cap_rows
+        self.drop_signal = False        # fault-injection aid for the timeout test
+        if device.type == "cuda":
+            if heap is None:
+                raise ValueError("a SymmetricHeap is required on CUDA")
+            self._build_engine()
+
+    # ---------------------------------------------------------------- weights
+    def load_reference_weights(self, w1: torch.Tensor, w3: Optional[torch.Tensor] = None,
+                               w2: Optional[torch.Tensor] = None) -> None:
+        with torch.no_grad():
+            if self.cfg.gated:
+                self.w13.copy_(cpu_ref.interleave_gate_up(w1.to(self.w13.device), w3.to(self.w13.device)))
+                self.w2.copy_(w2.to(self.w2.device).transpose(1, 2))
+            else:
+                self.w13.copy_(w1.to(self.w13.device).transpose(1, 2))
+
+    def reference_weights(self) -> Tuple[torch.Tensor, Optional[torch.Tensor], Optional[torch.Tensor]]:
+        """Weights in the ``x @ W`` layouts: (W1 [e,D,F], W3 [e,D,F], W2 [e,F,D]) or (W [e,D,N], None, None)."""
+        if not self.cfg.gated:
+            return self.w13.transpose(1, 2).contiguous(), None, None
+        EL, F2, D = self.w13.shape
+        blk = self.w13.view(EL, F2 // 256, 2, 128, D)
+        w1 = blk[:, :, 0].reshape(EL, F2 // 2, D).transpose(1, 2).contiguous()
+        w3 = blk[:, :, 1].reshape(EL, F2 // 2, D).transpose(1, 2).contiguous()
+        return w1, w3, self.w2.transpose(1, 2).contiguous()
+
+    # ----------------------------------------------------------------- engine
+    def _build_engine(self) -> None:
+        cfg, heap = self.cfg, self.heap
+        W, EL, ET, k, D = cfg.world_size, cfg.e_local, cfg.num_experts, cfg.topk, cfg.hidden_dim
+        if heap.world != W:
+            raise ValueError(f"heap spans {heap.world} ranks but the config says {W}")
+        if ET > nv.MAX_EXPERTS or EL > nv.MAX_GROUPS:
+            raise ValueError(f"at most {nv.MAX_EXPERTS} experts are supported")
+        if D % 8 or (cfg.gated and cfg.ffn_dim % 128):
+            raise ValueError("hidden_dim must be a multiple of 8 and ffn_dim of 128")
+        T = self.max_tokens
+        if T * k >= (1 << 24):
+            raise ValueError("max_tokens * topk must stay below 2^24")
+        dev = heap.device
+        cap = self._cap_rows if self._cap_rows is not None else default_cap_rows(cfg, T)
+        self.cap_rows = cap
+        self.cap_mtiles = cap // BM + EL + 1
+        u32 = torch.int32
+        # symmetric state (identical offsets on every rank)
+        self.recv = heap.empty((2, cap, D), cfg.dtype)
+        self.meta = heap.zeros((2, cap, 2), u32)
+        self.ready = heap.zeros((2, self.cap_mtiles), u32)
+        self.counts_all = heap.zeros((2, W, ET), u32)
+        self.counts_flag = heap.zeros((2, W), u32)
+        self.iter_done = heap.zeros((W,), u32)
+        self.out_slots = heap.empty((T * k, cfg.out_dim), cfg.dtype)
+        self.arrived = heap.zeros((1,), u32)
+        # local state
+        i32 = dict(dtype=torch.int32, device=dev)
+        self.hidden = (torch.empty((cap, cfg.ffn_dim), dtype=cfg.dtype, device=dev)
+                       if cfg.gated else None)
+        self.group_rows = torch.zeros(EL, **i32)
+        self.ticket = torch.zeros(1, **i32)
+        n = T * k
+        self._plan = Plan(torch.empty(ET, **i32), torch.empty(ET + 1, **i32), torch.empty(n, **i32),
+                          torch.empty(n, **i32), torch.empty(n, **i32))
+        self._slot_reduce = declare(
+            "b200_slot_reduce",
+            [C.c_void_p, C.c_void_p, C.c_uint, C.c_int, C.c_int, C.c_int, C.c_void_p,
+             C.POINTER(RetireArgs), C.c_void_p, C.c_ulonglong, C.c_void_p])
+        self._ctas = sm_count(dev)
+        self._budget_ns = int(cfg.wait_budget_ms * 1e6)
+        # every rank's buffers exist and are zeroed before anyone dispatches
+        torch.cuda.synchronize(dev)
+        if W > 1:
+            dist.barrier(group=heap.group)
+        self._engine_ready = True
+
+    @property
+    def status(self) -> torch.Tensor:
+        return self.heap.status
+
+    def check_status(self) -> None:
+        """Host-side check of the device status word (synchronises)."""
+        self.heap.check_status()
+
+    # ---------------------------------------------------------------- forward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if not x.is_cuda:
+            return self._forward_cpu(x)
+        return self._forward_fused(x)
+
+    def route(self, x: torch.Tensor):
+        return router_topk(x, self.router, self.cfg.topk, self.router_bias, self.cfg.renormalize)
+
+    def _forward_fused(self, x: torch.Tensor) -> torch.Tensor:
+        cfg, heap = self.cfg, self.heap
+        W, EL, ET, k, D = cfg.world_size, cfg.e_local, cfg.num_experts, cfg.topk, cfg.hidden_dim
+        T = x.shape[0]
+        if T > self.max_tokens or x.shape[1] != D:
+            raise ValueError(f"x must be [T <= {self.max_tokens}, {D}]")
+        if x.dtype != cfg.dtype or not x.is_contiguous():
+            x = x.to(cfg.dtype).contiguous()
+        it = self._iteration
+        par = it & 1
+        lib = nv.lib()
+        st = stream_ptr(x)
+        status_p = heap.status.data_ptr()
+
+        # 1. router
+        idx, wgt = self.route(x)
+
+        # 2. plan (+ counts push)
+        push = PlanPushArgs()
+        push.world, push.rank = W, heap.rank
+        push.epoch = it + 1
+        push.need_iter_done = max(0, it - 1)
+        push.iter_done = self.iter_done.data_ptr()
+        push.peer_counts = heap.peer_ptrs(self.counts_all[par])
+        push.peer_flags = heap.peer_ptrs(self.counts_flag[par])
+        push.status = status_p
+        push.wait_budget_ns = self._budget_ns
+        plan = self._plan
+        n = T * k
+        view = Plan(plan.counts, plan.bucket_start, plan.send_order[:n], plan.dst_slot[:n],
+                    plan.rank_in_bucket[:n])
+        make_plan(idx, ET, out=view, push=push)
+
+        # 3. dispatch + GEMM1 (one kernel)
+        da = nv.DispatchArgs()
+        da.world, da.rank, da.e_local, da.topk, da.num_tokens = W, heap.rank, EL, k, T
+        da.x = x.data_ptr()
+        da.send_order = plan.send_order.data_ptr()
+        da.topk_weight = wgt.data_ptr()
+        da.counts_all = self.counts_all[par].data_ptr()
+        da.counts_flag = self.counts_flag[par].data_ptr()
+        da.epoch = it + 1
+        da.cap_rows = self.cap_rows
+        da.drop_signal = int(self.drop_signal)
+        da.peer_recv = heap.peer_ptrs(self.recv[par])
+        da.peer_meta = heap.peer_ptrs(self.meta[par])
+        da.peer_ready = heap.peer_ptrs(self.ready[par])
+        da.group_rows_out = self.group_rows.data_ptr()
+
+        ca = nv.CombineArgs()
+        ca.world = W
+        ca.row_meta = self.meta[par].data_ptr()
+        ca.out_row_stride = cfg.out_dim
+        ca.max_slots = self.max_tokens * k
+        ca.peer_out = heap.peer_ptrs(self.out_slots)
+        ca.peer_arrived = heap.peer_ptrs(self.arrived)
+
+        ga = nv.GemmArgs()
+        ga.num_groups, ga.K, ga.group_m = EL, D, 16
+        ga.status, ga.wait_budget_ns = status_p, self._budget_ns
+        recv = self.recv[par]
+        if cfg.gated:
+            F = cfg.ffn_dim
+            ga.N, ga.n_out = 2 * F, F
+            ga.out, ga.ldo = self.hidden.data_ptr(), F
+            nv.check(lib.b200_grouped_gemm(ptr(recv), self.cap_rows, ptr(self.w13), nv.EPI_SILU_GATE, 1,
+                                           C.byref(ga), C.byref(da), None, self._ctas, st),
+                     "dispatch+GEMM1 launch")
+            # 4. GEMM2 + combine (one kernel)
+            gb = nv.GemmArgs()
+            gb.num_groups, gb.N, gb.K, gb.n_out, gb.group_m = EL, D, F, D, 16
+            gb.group_rows = self.group_rows.data_ptr()
+            gb.status, gb.wait_budget_ns = status_p, self._budget_ns
+            nv.check(lib.b200_grouped_gemm(ptr(self.hidden), self.cap_rows, ptr(self.w2), nv.EPI_COMBINE,
+                                           0, C.byref(gb), None, C.byref(ca), self._ctas, st),
+                     "GEMM2+combine launch")
+        else:
+            # single Linear: dispatch, GEMM and combine are ONE kernel
+            ga.N = ga.n_out = cfg.out_dim
+            nv.check(lib.b200_grouped_gemm(ptr(recv), self.cap_rows, ptr(self.w13), nv.EPI_COMBINE, 1,
+                                           C.byref(ga), C.byref(da), C.byref(ca), self._ctas, st),
+                     "dispatch+GEMM+combine launch")
+
+        # 5. slot reduce + retire
+        y = torch.empty((T, cfg.out_dim), dtype=cfg.dtype, device=x.device)
+        ra = RetireArgs()
+        ra.world, ra.rank = W, heap.rank
+        ra.iter_done_value = it + 1
+        ra.peer_iter_done = heap.peer_ptrs(self.iter_done)
+        ra.ready_counters = self.ready[par].data_ptr()
+        ra.num_ready = self.cap_mtiles
+        ra.ticket = self.ticket.data_ptr()
+        n_tiles = (cfg.out_dim + BN - 1) // BN
+        nv.check(self._slot_reduce(ptr(self.out_slots), ptr(self.arrived), T * k * n_tiles, T, k,
+                                   cfg.out_dim, ptr(y), C.byref(ra), C.c_void_p(status_p),
+                                   self._budget_ns, st), "slot reduce launch")
+        self._iteration = it + 1
+        self.last_routing = (idx, wgt)
+        return y
+
+    # -------------------------------------------------------------- CPU path
+    def _forward_cpu(self, x: torch.Tensor) -> torch.Tensor:
+        from ..parallel.gloo_moe import moe_forward_gloo
+        return moe_forward_gloo(self, x)
