@@ -354,6 +354,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int row0 = c.g_row_start[g] + m * BM;
       bool valid = row_in_tile < rows_in_tile;
 
+      // warp-uniform decision: the TMEM loads below need the whole warp
+      const bool got = mbar_wait(&c.tmem_full[acc], acc_phase, w, ST_TIMEOUT_TMEM_FULL);
+      if (!__all_sync(0xffffffffu, got)) break;
+      tc_fence_after_sync();
+      // Row metadata is read only now: in the fused-dispatch build it is written by the
+      // sending rank together with the row, and the accumulator being complete implies
+      // that the producer has seen the tile's arrival count.
       unsigned long long my_dst = 0;     // byte address of this thread's output row
       float wgt = 1.0f;
       int dst_rank = -1;
@@ -377,10 +384,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                  static_cast<unsigned long long>(row0 + row_in_tile) * ga.ldo * 2ull;
       }
 
-      // warp-uniform decision: the TMEM loads below need the whole warp
-      const bool got = mbar_wait(&c.tmem_full[acc], acc_phase, w, ST_TIMEOUT_TMEM_FULL);
-      if (!__all_sync(0xffffffffu, got)) break;
-      tc_fence_after_sync();
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 
 #pragma unroll 1

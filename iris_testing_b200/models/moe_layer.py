@@ -193,6 +193,11 @@ class MoELayer(nn.Module):
         self._engine_ready = True
 
     @property
+    def launches_per_forward(self) -> int:
+        """Kernel launches of one fused forward: router, plan (2), fused GEMM kernel(s), slot reduce."""
+        return 6 if self.cfg.gated else 5
+
+    @property
     def status(self) -> torch.Tensor:
         return self.heap.status
 
