@@ -1,0 +1,90 @@
+"""GPU tests of the fused MoE layer (single GPU: every "peer" is the local GPU)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _make(cfg, T, **kw):
+    from iris_testing_b200.models import MoELayer, heap_bytes_needed
+    from iris_testing_b200.parallel.symm import SymmetricHeap
+    torch.cuda.set_device(0)
+    heap = SymmetricHeap(heap_bytes_needed(cfg, T, kw.get("cap_rows")) + (16 << 20),
+                         wait_budget_ms=kw.pop("budget", 2000.0))
+    return MoELayer(cfg, max_tokens=T, heap=heap, router_std=None, **kw), heap
+
+
+def _dense(layer, x):
+    from iris_testing_b200.ops import cpu_ref
+    cfg = layer.cfg
+    w1, w3, w2 = layer.reference_weights()
+    if cfg.gated:
+        return cpu_ref.dense_moe_ref(x, layer.router, cfg.topk, w1=w1, w3=w3, w2=w2,
+                                     bias=layer.router_bias, round_hidden=torch.bfloat16)
+    return cpu_ref.dense_moe_ref(x, layer.router, cfg.topk, w_single=w1, bias=layer.router_bias)
+
+
+@pytest.mark.parametrize("D,F,E,k,gated,T", [
+    (256, 512, 8, 2, True, 200), (256, 0, 4, 1, False, 77), (2048, 1408, 32, 4, True, 2048),
+    (512, 256, 64, 8, True, 1000), (128, 0, 8, 2, False, 128)])
+def test_fused_layer_matches_dense_reference(D, F, E, k, gated, T):
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.utils import gen_local_tokens
+    cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=E, topk=k, gated=gated)
+    layer, heap = _make(cfg, T)
+    dev = heap.device
+    for i in range(3):                                  # exercises both parity slots and re-arming
+        x = gen_local_tokens(1, T, D, torch.bfloat16, dev, i, 0, "normal")
+        y = layer(x)
+        ref = _dense(layer, x)
+        assert torch.allclose(y.float(), ref, atol=3e-2 * float(ref.abs().max()), rtol=3e-2), i
+    layer.check_status()
+    y_short = layer(x[: T // 2])                        # fewer tokens than max_tokens
+    assert torch.allclose(y_short.float(), ref[: T // 2], atol=3e-2 * float(ref.abs().max()), rtol=3e-2)
+    layer.check_status()
+
+
+def test_fused_layer_skewed_routing_and_empty_experts():
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.utils import gen_local_tokens, zipf_expert_bias
+    cfg = MoEConfig(hidden_dim=256, ffn_dim=256, num_experts=16, topk=2)
+    layer, heap = _make(cfg, 600)
+    layer.router_bias = zipf_expert_bias(16, 1.2, scale=4.0, device=heap.device)
+    x = gen_local_tokens(1, 600, 256, torch.bfloat16, heap.device, 3, 0, "normal")
+    y = layer(x)
+    ref = _dense(layer, x)
+    rows = layer.group_rows.cpu()
+    assert int(rows.sum()) == 1200 and int(rows.max()) > 4 * max(int(rows.min()), 1)
+    assert torch.allclose(y.float(), ref, atol=3e-2 * float(ref.abs().max()), rtol=3e-2)
+    layer.check_status()
+
+
+def test_capacity_overflow_is_reported_not_written():
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.utils import gen_local_tokens
+    cfg = MoEConfig(hidden_dim=128, ffn_dim=128, num_experts=4, topk=2)
+    layer, heap = _make(cfg, 512, cap_rows=256, budget=100.0)      # 1024 routed rows > 256
+    x = gen_local_tokens(1, 512, 128, torch.bfloat16, heap.device, 0, 0, "normal")
+    layer(x)
+    torch.cuda.synchronize()
+    with pytest.raises(Exception, match="overflow"):
+        layer.check_status()
+
+
+def test_dropped_arrival_signal_times_out_with_status():
+    """Host-injected fault: the senders skip the tile-arrival signal.  The consumer's wait
+    runs out of budget, the kernels drain and return, and the host reads the status."""
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.utils import gen_local_tokens
+    cfg = MoEConfig(hidden_dim=128, ffn_dim=128, num_experts=4, topk=2, wait_budget_ms=50.0)
+    layer, heap = _make(cfg, 256, budget=50.0)
+    x = gen_local_tokens(1, 256, 128, torch.bfloat16, heap.device, 0, 0, "normal")
+    layer(x)
+    layer.check_status()
+    layer.drop_signal = True
+    layer(x)
+    torch.cuda.synchronize()
+    with pytest.raises(Exception, match="never arrived"):
+        layer.check_status()
+    # the context is still usable
+    assert float(torch.ones(4, device=heap.device).sum()) == 4.0
