@@ -274,3 +274,54 @@ int b200_pack_rows(const void* x, const int* send_order, int n_flat, int topk, i
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free plan (declared and documented in plan_noalloc.h).
+// ---------------------------------------------------------------------------
+#include "plan_noalloc.h"
+
+namespace b200 {
+// The temporary of the plan kernels (one int per routed copy).  In host code
+// this name is only a handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) int g_plan_scratch[B200_PLAN_NOALLOC_MAX];
+
+constexpr int kMaxDevices = 64;
+static int* g_plan_scratch_addr[kMaxDevices] = {nullptr};
+}  // namespace b200
+
+extern "C" {
+
+int b200_plan_noalloc_max(void) { return B200_PLAN_NOALLOC_MAX; }
+
+int b200_plan_noalloc(const int* topk_idx, int n_flat, int num_experts, int* counts,
+                      int* bucket_start, int* send_order, int* dst_slot, void* stream) {
+  if (n_flat < 0 || num_experts < 1 || num_experts > B200_MAX_EXPERTS || topk_idx == nullptr ||
+      counts == nullptr || bucket_start == nullptr || send_order == nullptr)
+    return B200_PLAN_NOALLOC_BAD_ARG;
+  if (n_flat > B200_PLAN_NOALLOC_MAX) return B200_PLAN_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (dev < 0 || dev >= b200::kMaxDevices) return B200_PLAN_NOALLOC_NO_DEVICE;
+  // once per device, with that device current: resolve the array's device address
+  if (b200::g_plan_scratch_addr[dev] == nullptr) {
+    int* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), b200::g_plan_scratch);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (p == nullptr) return B200_PLAN_NOALLOC_NO_DEVICE;
+    b200::g_plan_scratch_addr[dev] = p;
+  }
+  int* scratch = b200::g_plan_scratch_addr[dev];
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  b200::plan_rank_kernel<<<num_experts, 1024, 0, st>>>(topk_idx, n_flat, num_experts, scratch, counts);
+  b200::PlanPushArgs pz;
+  memset(&pz, 0, sizeof(pz));
+  int blocks = (n_flat + 255) / 256;
+  if (blocks < 1) blocks = 1;
+  if (blocks > 1184) blocks = 1184;
+  b200::plan_finalize_kernel<<<blocks, 256, 0, st>>>(topk_idx, scratch, counts, n_flat, num_experts,
+                                                     bucket_start, send_order, dst_slot, pz, 0);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"
