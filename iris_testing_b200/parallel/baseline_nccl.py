@@ -138,6 +138,7 @@ class AllToAllMoEBaseline:
     def __init__(self, layer, group=None) -> None:
         self.layer = layer
         self.group = group
+        self._weights = None      # x @ W layouts, materialised once
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor) -> torch.Tensor:
@@ -149,7 +150,9 @@ class AllToAllMoEBaseline:
         send_counts = plan.counts.view(world, EL)
         recv_counts = exchange_counts(send_counts, self.group)
         recv, ins, outs = exchange_payload(payload, send_counts, recv_counts, None, self.group)
-        w1, w3, w2 = layer.reference_weights()
+        if self._weights is None:
+            self._weights = layer.reference_weights()
+        w1, w3, w2 = self._weights
         out = recv.new_empty(recv.shape[0], cfg.out_dim)
         rc = recv_counts.tolist()
         off = 0
