@@ -18,6 +18,7 @@ MAX_EXPERTS = 128
 EPI_STORE = 0
 EPI_SILU_GATE = 1
 EPI_COMBINE = 2
+EPI_ROUTER = 3
 
 STATUS_NAMES = {
     0: "ok",
@@ -85,6 +86,19 @@ class GemmArgs(C.Structure):
         ("ldo", C.c_longlong),
         ("status", C.c_void_p),
         ("wait_budget_ns", C.c_ulonglong),
+        ("single_group_rows", C.c_int),
+        ("mma_n", C.c_int),
+    ]
+
+
+class RouterArgs(C.Structure):
+    _fields_ = [
+        ("num_experts", C.c_int),
+        ("topk", C.c_int),
+        ("renorm", C.c_int),
+        ("bias", C.c_void_p),
+        ("topk_idx", C.c_void_p),
+        ("topk_w", C.c_void_p),
     ]
 
 
@@ -104,7 +118,7 @@ def _declare(lib: C.CDLL) -> None:
     vp, i32, i64, u64 = C.c_void_p, C.c_int, C.c_longlong, C.c_ulonglong
     sigs = {
         "b200_grouped_gemm": ([vp, i64, vp, i32, i32, C.POINTER(GemmArgs), C.POINTER(DispatchArgs),
-                               C.POINTER(CombineArgs), i32, vp], i32),
+                               C.POINTER(CombineArgs), C.POINTER(RouterArgs), i32, vp], i32),
         "b200_gemm_smem_bytes": ([], i32),
     }
     for name, (argtypes, restype) in sigs.items():

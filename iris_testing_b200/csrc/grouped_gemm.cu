@@ -31,6 +31,7 @@
 
 #include "moe_args.h"
 #include "sm100_ptx.cuh"
+#include "topk.cuh"
 
 namespace b200 {
 
@@ -137,9 +138,15 @@ __device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200
     for (int s = 0; s < W; ++s) rows += __ldcg(cnt + ((s * W + me) * EL + e));
     c.g_rows[e] = rows;
   }
+  // Buckets are visited expert-major, and inside an expert destination-rotated starting
+  // with this rank: every rank's expert 0 fills first, each from its nearest "upstream"
+  // ranks first.  The receive layout orders the source segments of an expert the same
+  // way (self, self-1, self-2, ... modulo the world), so rows land in the order the
+  // consumer's M-tiles need them.
   for (int bi = tid; bi < ET; bi += nthreads) {
-    const int ge = (me * EL + bi) % ET;     // start with this rank's own experts
-    const int dst = ge / EL, e = ge - dst * EL;
+    const int e = bi / W, r = bi - e * W;
+    const int dst = (me + r) % W;
+    const int ge = dst * EL + e;
     const int n = __ldcg(cnt + ((me * W + dst) * EL + e));
     int send_start = 0;
     for (int q = 0; q < ge; ++q) send_start += __ldcg(cnt + (me * ET + q));
@@ -150,8 +157,8 @@ __device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200
       group_start += rows;
       mtile0 += (rows + BM - 1) / BM;
     }
-    int within = 0;
-    for (int s = 0; s < me; ++s) within += __ldcg(cnt + ((s * W + dst) * EL + e));
+    int within = 0;   // rows of the sources that precede this rank in dst's segment order
+    for (int q = 0; q < r; ++q) within += __ldcg(cnt + ((((dst - q + W) % W) * W + dst) * EL + e));
     c.b_count[bi] = n;
     c.b_send_start[bi] = send_start;
     c.b_dst_row[bi] = group_start + within;
@@ -171,7 +178,8 @@ template <int EPI, bool FUSED>
 __global__ void __launch_bounds__(FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, const b200_gemm_args ga,
-                    const b200_dispatch_args da, const b200_combine_args ca) {
+                    const b200_dispatch_args da, const b200_combine_args ca,
+                    const b200_router_args ra) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -236,7 +244,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       da.group_rows_out[tid] = c.g_rows[tid];
   } else {
     for (int g = tid; g < G; g += nthreads) {
-      int r = ga.group_rows[g];
+      int r = ga.group_rows != nullptr ? ga.group_rows[g] : ga.single_group_rows;
       c.g_rows[g] = r < 0 ? 0 : r;
     }
   }
@@ -302,7 +310,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16_f32(BM, BN);
+      const uint32_t idesc = make_idesc_bf16_f32(BM, ga.mma_n > 0 ? ga.mma_n : BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
@@ -385,6 +393,59 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
 
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
+
+      if constexpr (EPI == B200_EPI_ROUTER) {
+        // One thread owns one token: its logits are the first E columns of the accumulator.
+        const int E = ra.num_experts;
+        float mx = -CUDART_INF_F;
+        for (int c0 = 0; c0 < E; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_acc + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < E)
+              mx = fmaxf(mx, __uint_as_float(v[j]) + (ra.bias != nullptr ? __ldg(ra.bias + c0 + j) : 0.f));
+        }
+        TopK tk;
+        tk.init();
+        float sum = 0.f;
+        for (int c0 = 0; c0 < E; c0 += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32b_x32(t_acc + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (c0 + j < E) {
+              const float lg = __uint_as_float(v[j]) + (ra.bias != nullptr ? __ldg(ra.bias + c0 + j) : 0.f);
+              sum += __expf(lg - mx);
+              tk.push(lg, c0 + j);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&c.tmem_empty[acc]);
+        if (valid) {
+          const float inv = 1.0f / sum;
+          float p[ROUTER_MAX_K];
+          float psum = 0.f;
+#pragma unroll
+          for (int j = 0; j < ROUTER_MAX_K; ++j) {
+            p[j] = (j < ra.topk) ? __expf(tk.v[j] - mx) * inv : 0.f;
+            psum += p[j];
+          }
+          const float scale = ra.renorm ? 1.0f / psum : 1.0f;
+          const size_t o = static_cast<size_t>(row0 + row_in_tile) * ra.topk;
+#pragma unroll
+          for (int j = 0; j < ROUTER_MAX_K; ++j) {
+            if (j < ra.topk) {
+              ra.topk_idx[o + j] = tk.i[j];
+              ra.topk_w[o + j] = p[j] * scale;
+            }
+          }
+        }
+        continue;
+      }
 
 #pragma unroll 1
       for (int p = 0; p < PASSES; ++p) {
@@ -486,17 +547,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           const uint4* src = reinterpret_cast<const uint4*>(da.x) + static_cast<size_t>(t) * k16;
           uint4* out = reinterpret_cast<uint4*>(recv + static_cast<size_t>(drow) * ga.K * 2);
-          for (int i = lane; i < k16; i += 128) {
-            uint4 v0, v1, v2, v3;
-            const bool h1 = i + 32 < k16, h2 = i + 64 < k16, h3 = i + 96 < k16;
-            v0 = ld_nc_16(src + i);
-            if (h1) v1 = ld_nc_16(src + i + 32);
-            if (h2) v2 = ld_nc_16(src + i + 64);
-            if (h3) v3 = ld_nc_16(src + i + 96);
-            st_16(out + i, v0);
-            if (h1) st_16(out + i + 32, v1);
-            if (h2) st_16(out + i + 64, v2);
-            if (h3) st_16(out + i + 96, v3);
+          for (int i = lane; i < k16; i += 256) {
+            uint4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (i + 32 * j < k16) v[j] = ld_nc_16(src + i + 32 * j);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (i + 32 * j < k16) st_16(out + i + 32 * j, v[j]);
           }
           if (lane == 0) {
             uint2 mv;
@@ -564,8 +622,8 @@ static int make_tmap_bf16(CUtensorMap* tm, const void* base, long long rows, lon
 
 template <int EPI, bool FUSED>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const b200_gemm_args& ga,
-                          const b200_dispatch_args& da, const b200_combine_args& ca, int ctas,
-                          cudaStream_t stream) {
+                          const b200_dispatch_args& da, const b200_combine_args& ca,
+                          const b200_router_args& ra, int ctas, cudaStream_t stream) {
   static bool configured = false;
   auto kern = grouped_gemm_kernel<EPI, FUSED>;
   if (!configured) {
@@ -573,7 +631,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const b2
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  kern<<<ctas, FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, SMEM_BYTES, stream>>>(ta, tb, ga, da, ca);
+  kern<<<ctas, FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, SMEM_BYTES, stream>>>(ta, tb, ga, da, ca, ra);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -587,15 +645,21 @@ extern "C" {
 // (cudaError_t) error code.  Nothing is allocated.
 int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, int fused,
                       const b200_gemm_args* ga, const b200_dispatch_args* da,
-                      const b200_combine_args* ca, int num_ctas, void* stream) {
+                      const b200_combine_args* ca, const b200_router_args* ra, int num_ctas,
+                      void* stream) {
   using namespace b200;
-  if (ga == nullptr || ga->K % 8 != 0 || ga->N % 8 != 0 || ga->n_out % 8 != 0) return -10;
+  if (ga == nullptr || ga->K % 8 != 0) return -10;
+  if (epi != B200_EPI_ROUTER && (ga->N % 8 != 0 || ga->n_out % 8 != 0)) return -10;
   const int G = fused ? (da ? da->e_local : 0) : ga->num_groups;
   if (G <= 0 || G > B200_MAX_GROUPS) return -11;
   if (fused && (da == nullptr || da->world * da->e_local > B200_MAX_EXPERTS ||
                 da->world > B200_MAX_WORLD))
     return -12;
   if (epi == B200_EPI_COMBINE && ca == nullptr) return -13;
+  if (epi == B200_EPI_ROUTER && (ra == nullptr || ra->num_experts > BN || ra->num_experts < 1 ||
+                                 ra->topk < 1 || ra->topk > ROUTER_MAX_K || ra->topk > ra->num_experts))
+    return -16;
+  if (ga->mma_n != 0 && (ga->mma_n % 16 != 0 || ga->mma_n < 16 || ga->mma_n > BN)) return -17;
   CUtensorMap ta, tb;
   int r = make_tmap_bf16(&ta, a, a_rows, ga->K, BM);
   if (r != 0) return r;
@@ -603,23 +667,27 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
   if (r != 0) return r - 10;
   b200_dispatch_args dz;
   b200_combine_args cz;
+  b200_router_args rz;
   memset(&dz, 0, sizeof(dz));
   memset(&cz, 0, sizeof(cz));
+  memset(&rz, 0, sizeof(rz));
+  const b200_router_args& r2 = ra ? *ra : rz;
   const b200_dispatch_args& d = da ? *da : dz;
   const b200_combine_args& c = ca ? *ca : cz;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (num_ctas <= 0) return -14;
   if (!fused) {
     switch (epi) {
-      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, false>(ta, tb, *ga, d, c, num_ctas, st);
-      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, false>(ta, tb, *ga, d, c, num_ctas, st);
-      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, false>(ta, tb, *ga, d, c, num_ctas, st);
+      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, false>(ta, tb, *ga, d, c, r2, num_ctas, st);
+      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, false>(ta, tb, *ga, d, c, r2, num_ctas, st);
+      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, false>(ta, tb, *ga, d, c, r2, num_ctas, st);
+      case B200_EPI_ROUTER: return launch_variant<B200_EPI_ROUTER, false>(ta, tb, *ga, d, c, r2, num_ctas, st);
     }
   } else {
     switch (epi) {
-      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, true>(ta, tb, *ga, d, c, num_ctas, st);
-      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, true>(ta, tb, *ga, d, c, num_ctas, st);
-      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, true>(ta, tb, *ga, d, c, num_ctas, st);
+      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, true>(ta, tb, *ga, d, c, r2, num_ctas, st);
+      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, true>(ta, tb, *ga, d, c, r2, num_ctas, st);
+      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, true>(ta, tb, *ga, d, c, r2, num_ctas, st);
     }
   }
   return -15;

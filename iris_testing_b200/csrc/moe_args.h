@@ -13,6 +13,7 @@
 #define B200_EPI_STORE 0       // out[row, n]            = acc
 #define B200_EPI_SILU_GATE 1   // out[row, n]            = silu(acc_gate) * acc_up
 #define B200_EPI_COMBINE 2     // peer_out[src][slot, n] = weight(row) * acc
+#define B200_EPI_ROUTER 3      // per row: softmax over the N logits, then top-k (idx, weight)
 
 #ifdef __cplusplus
 extern "C" {
@@ -60,7 +61,19 @@ typedef struct {
   long long ldo;                  // EPI 0/1 output row stride (elements)
   int* status;                    // this rank's status word
   unsigned long long wait_budget_ns;
+  int single_group_rows;          // used when group_rows is null: one group of this many rows
+  int mma_n;                      // N of the MMA instruction (multiple of 16, <= 256); 0 = 256
 } b200_gemm_args;
+
+// Router epilogue: the accumulator row holds the logits of one token.
+typedef struct {
+  int num_experts;                // E (<= 256): columns of the accumulator that are logits
+  int topk;                       // k (<= 8)
+  int renorm;                     // renormalise the k weights to sum to 1
+  const float* bias;              // [E] added to the logits, or null
+  int* topk_idx;                  // [rows, k]
+  float* topk_w;                  // [rows, k]
+} b200_router_args;
 
 #ifdef __cplusplus
 }

@@ -280,7 +280,7 @@ class MoELayer(nn.Module):
             ga.N, ga.n_out = 2 * F, F
             ga.out, ga.ldo = self.hidden.data_ptr(), F
             nv.check(lib.b200_grouped_gemm(ptr(recv), self.cap_rows, ptr(self.w13), nv.EPI_SILU_GATE, 1,
-                                           C.byref(ga), C.byref(da), None, self._ctas, st),
+                                           C.byref(ga), C.byref(da), None, None, self._ctas, st),
                      "dispatch+GEMM1 launch")
             # 4. GEMM2 + combine (one kernel)
             gb = nv.GemmArgs()
@@ -288,13 +288,13 @@ class MoELayer(nn.Module):
             gb.group_rows = self.group_rows.data_ptr()
             gb.status, gb.wait_budget_ns = status_p, self._budget_ns
             nv.check(lib.b200_grouped_gemm(ptr(self.hidden), self.cap_rows, ptr(self.w2), nv.EPI_COMBINE,
-                                           0, C.byref(gb), None, C.byref(ca), self._ctas, st),
+                                           0, C.byref(gb), None, C.byref(ca), None, self._ctas, st),
                      "GEMM2+combine launch")
         else:
             # single Linear: dispatch, GEMM and combine are ONE kernel
             ga.N = ga.n_out = cfg.out_dim
             nv.check(lib.b200_grouped_gemm(ptr(recv), self.cap_rows, ptr(self.w13), nv.EPI_COMBINE, 1,
-                                           C.byref(ga), C.byref(da), C.byref(ca), self._ctas, st),
+                                           C.byref(ga), C.byref(da), C.byref(ca), None, self._ctas, st),
                      "dispatch+GEMM+combine launch")
 
         # 5. slot reduce + retire

@@ -85,7 +85,7 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     ga.wait_budget_ns = int(wait_budget_ms * 1e6)
     ctas = num_ctas or sm_count(a.device)
     rc = nv.lib().b200_grouped_gemm(ptr(a), M, ptr(w_kmajor), epilogue, 0, C.byref(ga), None, None,
-                                    ctas, stream_ptr(a))
+                                    None, ctas, stream_ptr(a))
     nv.check(rc, "grouped_gemm launch")
     return out
 

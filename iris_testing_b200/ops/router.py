@@ -19,8 +19,13 @@ MAX_TOPK = 8
 
 def router_topk(x: torch.Tensor, w_router: torch.Tensor, topk: int,
                 bias: Optional[torch.Tensor] = None, renormalize: bool = False,
-                return_logits: bool = False):
-    """x [T, D], w_router [D, E] -> (idx int32 [T, k], weight fp32 [T, k][, logits fp32 [T, E]])."""
+                return_logits: bool = False, force_simple: bool = False,
+                status: Optional[torch.Tensor] = None):
+    """x [T, D], w_router [D, E] -> (idx int32 [T, k], weight fp32 [T, k][, logits fp32 [T, E]]).
+
+    On CUDA the logits are computed on the tensor cores and softmax/top-k run in that
+    kernel's epilogue (hidden_dim % 8 == 0 and E <= 256); other shapes, ``return_logits``
+    and ``force_simple`` take a CUDA-core kernel."""
     require(x.dim() == 2 and w_router.dim() == 2 and x.shape[1] == w_router.shape[0],
             "router_topk: x must be [T, D] and w_router [D, E]")
     T, D = x.shape
@@ -34,15 +39,61 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, topk: int,
         return idx, w
     x = contiguous_bf16(x, "x")
     w_router = contiguous_bf16(w_router, "w_router")
+    idx = torch.empty((T, topk), dtype=torch.int32, device=x.device)
+    w = torch.empty((T, topk), dtype=torch.float32, device=x.device)
+    b = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
+    if T == 0:
+        return (idx, w, torch.empty((0, E), dtype=torch.float32, device=x.device)) if return_logits else (idx, w)
+    if not return_logits and not force_simple and D % 8 == 0 and E <= 256:
+        _router_tensor_core(x, router_kmajor(w_router), b, topk, renormalize, idx, w, status)
+        return idx, w
     fn = declare("b200_router_topk_simple",
                  [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                   C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p])
-    idx = torch.empty((T, topk), dtype=torch.int32, device=x.device)
-    w = torch.empty((T, topk), dtype=torch.float32, device=x.device)
     logits = torch.empty((T, E), dtype=torch.float32, device=x.device) if return_logits else None
-    b = None if bias is None else bias.to(device=x.device, dtype=torch.float32).contiguous()
     rc = fn(ptr(x), ptr(w_router), ptr(b), T, D, E, topk, int(renormalize), ptr(idx), ptr(w),
             ptr(logits), stream_ptr(x))
     if rc != 0:
         raise RuntimeError(f"router_topk launch failed ({rc})")
     return (idx, w, logits) if return_logits else (idx, w)
+
+
+_KMAJOR_CACHE = {}
+
+
+def router_kmajor(w_router: torch.Tensor) -> torch.Tensor:
+    """[D, E] -> contiguous [E, D] (the layout the tensor-core router reads), cached per
+    (storage, version) so that an unchanged parameter is transposed once."""
+    key = (w_router.data_ptr(), tuple(w_router.shape), w_router._version)
+    hit = _KMAJOR_CACHE.get(key)
+    if hit is None:
+        if len(_KMAJOR_CACHE) > 64:
+            _KMAJOR_CACHE.clear()
+        hit = w_router.t().contiguous()
+        _KMAJOR_CACHE[key] = hit
+    return hit
+
+
+def _router_tensor_core(x, wr_kmajor, bias, topk, renormalize, idx, w, status=None) -> None:
+    """Logits on tcgen05 (the grouped GEMM with one group and a narrow MMA), softmax and
+    top-k in the epilogue: each epilogue thread owns one token's accumulator row."""
+    from .. import _native as nv
+    from .expert import sm_count
+    T, D = x.shape
+    E = wr_kmajor.shape[0]
+    if status is None:
+        status = torch.zeros(4, dtype=torch.int32, device=x.device)
+    ga = nv.GemmArgs()
+    ga.num_groups, ga.N, ga.K, ga.n_out, ga.group_m = 1, E, D, E, 16
+    ga.group_rows = None
+    ga.single_group_rows = T
+    ga.mma_n = max(16, (E + 15) // 16 * 16)
+    ga.status = status.data_ptr()
+    ga.wait_budget_ns = int(2e9)
+    ra = nv.RouterArgs()
+    ra.num_experts, ra.topk, ra.renorm = E, topk, int(renormalize)
+    ra.bias = None if bias is None else bias.data_ptr()
+    ra.topk_idx, ra.topk_w = idx.data_ptr(), w.data_ptr()
+    rc = nv.lib().b200_grouped_gemm(ptr(x), T, ptr(wr_kmajor), nv.EPI_ROUTER, 0, C.byref(ga), None, None,
+                                    C.byref(ra), sm_count(x.device), stream_ptr(x))
+    nv.check(rc, "tensor-core router launch")

@@ -25,26 +25,33 @@ def test_native_library_is_loaded():
     assert "libb200moe.so" in maps
 
 
+@pytest.mark.parametrize("simple", [False, True])
 @pytest.mark.parametrize("T,D,E,k,bias", [(64, 128, 8, 2, False), (1000, 256, 64, 8, False),
-                                          (333, 512, 128, 4, True), (5, 64, 3, 1, False)])
-def test_router_topk(dev, T, D, E, k, bias):
+                                          (333, 512, 128, 4, True), (5, 64, 3, 1, False),
+                                          (4096, 2048, 256, 8, True)])
+def test_router_topk(dev, T, D, E, k, bias, simple):
     from iris_testing_b200.ops import cpu_ref, router_topk
     from iris_testing_b200.utils import gen_local_tokens, gen_router, zipf_expert_bias
     x = gen_local_tokens(1, T, D, torch.bfloat16, dev, 0, 0, "normal")
     wr = gen_router(D, E, torch.bfloat16, dev, 0, std=None)
     b = zipf_expert_bias(E, device=dev) if bias else None
-    idx, w, lg = router_topk(x, wr, k, bias=b, return_logits=True)
-    ridx, rw = cpu_ref.router_topk_ref(x, wr, k, bias=b)
     ref_lg = x.float() @ wr.float() + (b if bias else 0)
-    assert torch.allclose(lg, ref_lg, atol=1e-4, rtol=1e-4)
+    if simple:
+        idx, w, lg = router_topk(x, wr, k, bias=b, return_logits=True)
+        assert torch.allclose(lg, ref_lg, atol=1e-4, rtol=1e-4)
+    else:                                   # tensor-core path (softmax + top-k in the epilogue)
+        status = torch.zeros(4, dtype=torch.int32, device=dev)
+        idx, w = router_topk(x, wr, k, bias=b, status=status)
+        assert status[0].item() == 0
+    ridx, rw = cpu_ref.router_topk_ref(x, wr, k, bias=b)
     # near-ties may legitimately swap: compare where the reference's k-th gap is clear
     probs = torch.softmax(ref_lg, -1)
     srt = torch.sort(probs, -1, descending=True).values
     clear = (srt[:, :k] - srt[:, 1:k + 1]).min(dim=1).values > 1e-6 if E > k else torch.ones(T, dtype=torch.bool, device=dev)
     assert clear.float().mean() > 0.95
     assert torch.equal(idx[clear], ridx[clear])
-    assert torch.allclose(w[clear], rw[clear], atol=1e-6, rtol=1e-4)
-    _, wn = router_topk(x, wr, k, bias=b, renormalize=True)
+    assert torch.allclose(w[clear], rw[clear], atol=1e-6, rtol=2e-4)
+    _, wn = router_topk(x, wr, k, bias=b, renormalize=True, force_simple=simple)
     assert torch.allclose(wn.sum(-1), torch.ones(T, device=dev), atol=1e-5)
 
 
