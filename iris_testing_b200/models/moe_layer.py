@@ -119,6 +119,8 @@ class MoELayer(nn.Module):
         self._engine_ready = False
         self._cap_rows = cap_rows
         self.drop_signal = False        # fault-injection aid for the timeout test
+        self.profile = False            # record CUDA events between the phases of forward()
+        self.phase_events = []
         if device.type == "cuda":
             if heap is None:
                 raise ValueError("a SymmetricHeap is required on CUDA")
@@ -228,8 +230,13 @@ class MoELayer(nn.Module):
         st = stream_ptr(x)
         status_p = heap.status.data_ptr()
 
+        ev = self._mark if self.profile else (lambda name: None)
+        if self.profile:
+            self.phase_events = []
+        ev("start")
         # 1. router
         idx, wgt = self.route(x)
+        ev("router")
 
         # 2. plan (+ counts push)
         push = PlanPushArgs()
@@ -246,6 +253,7 @@ class MoELayer(nn.Module):
         view = Plan(plan.counts, plan.bucket_start, plan.send_order[:n], plan.dst_slot[:n],
                     plan.rank_in_bucket[:n])
         make_plan(idx, ET, out=view, push=push)
+        ev("plan")
 
         # 3. dispatch + GEMM1 (one kernel)
         da = nv.DispatchArgs()
@@ -282,6 +290,7 @@ class MoELayer(nn.Module):
             nv.check(lib.b200_grouped_gemm(ptr(recv), self.cap_rows, ptr(self.w13), nv.EPI_SILU_GATE, 1,
                                            C.byref(ga), C.byref(da), None, None, self._ctas, st),
                      "dispatch+GEMM1 launch")
+            ev("dispatch+gemm1")
             # 4. GEMM2 + combine (one kernel)
             gb = nv.GemmArgs()
             gb.num_groups, gb.N, gb.K, gb.n_out, gb.group_m = EL, D, F, D, 16
@@ -290,12 +299,14 @@ class MoELayer(nn.Module):
             nv.check(lib.b200_grouped_gemm(ptr(self.hidden), self.cap_rows, ptr(self.w2), nv.EPI_COMBINE,
                                            0, C.byref(gb), None, C.byref(ca), None, self._ctas, st),
                      "GEMM2+combine launch")
+            ev("gemm2+combine")
         else:
             # single Linear: dispatch, GEMM and combine are ONE kernel
             ga.N = ga.n_out = cfg.out_dim
             nv.check(lib.b200_grouped_gemm(ptr(recv), self.cap_rows, ptr(self.w13), nv.EPI_COMBINE, 1,
                                            C.byref(ga), C.byref(da), C.byref(ca), None, self._ctas, st),
                      "dispatch+GEMM+combine launch")
+            ev("dispatch+gemm+combine")
 
         # 5. slot reduce + retire
         y = torch.empty((T, cfg.out_dim), dtype=cfg.dtype, device=x.device)
@@ -310,9 +321,23 @@ class MoELayer(nn.Module):
         nv.check(self._slot_reduce(ptr(self.out_slots), ptr(self.arrived), T * k * n_tiles, T, k,
                                    cfg.out_dim, ptr(y), C.byref(ra), C.c_void_p(status_p),
                                    self._budget_ns, st), "slot reduce launch")
+        ev("slot_reduce")
         self._iteration = it + 1
         self.last_routing = (idx, wgt)
         return y
+
+    def _mark(self, name: str) -> None:
+        e = torch.cuda.Event(enable_timing=True)
+        e.record()
+        self.phase_events.append((name, e))
+
+    def phase_times_us(self) -> dict:
+        """Device time of each phase of the last profiled forward (synchronises)."""
+        torch.cuda.synchronize()
+        out = {}
+        for (_, a), (name, b) in zip(self.phase_events[:-1], self.phase_events[1:]):
+            out[name] = a.elapsed_time(b) * 1000.0
+        return out
 
     # -------------------------------------------------------------- CPU path
     def _forward_cpu(self, x: torch.Tensor) -> torch.Tensor:
