@@ -88,6 +88,7 @@ class GemmArgs(C.Structure):
         ("wait_budget_ns", C.c_ulonglong),
         ("single_group_rows", C.c_int),
         ("mma_n", C.c_int),
+        ("cta_pair", C.c_int),
     ]
 
 

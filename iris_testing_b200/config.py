@@ -25,6 +25,7 @@ class MoEConfig:
     dtype: torch.dtype = torch.bfloat16
     capacity_factor: Optional[float] = None   # None: worst case (every token of every rank)
     wait_budget_ms: float = 2000.0  # budget of every bounded device-side wait
+    cta_pair: Optional[bool] = None  # two CTAs per MMA (cta_group::2); None: when experts average >= 256 rows
 
     def __post_init__(self) -> None:
         if self.num_experts % self.world_size != 0:

@@ -38,11 +38,9 @@ namespace b200 {
 constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int STAGES = 4;
+constexpr int MAX_STAGES = 6;
 constexpr int UMMA_K = 16;
-constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KiB
-constexpr int B_STAGE_BYTES = BN * BK * 2;            // 32 KiB
-constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KiB per CTA
 constexpr int STG_COLS = 64;                          // columns per epilogue pass
 constexpr int STG_ROW_BYTES = STG_COLS * 2 + 16;      // padded: conflict-free 16 B stores
 constexpr int STG_BYTES = BM * STG_ROW_BYTES;         // 18 KiB
@@ -51,8 +49,8 @@ constexpr int NUM_THREADS_PLAIN = 192;
 constexpr int NUM_THREADS_FUSED = 320;
 
 struct __align__(16) ControlSmem {
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
+  uint64_t full[MAX_STAGES];
+  uint64_t empty[MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint64_t drain;
@@ -62,7 +60,9 @@ struct __align__(16) ControlSmem {
   int total_units;
   int g_rows[B200_MAX_GROUPS];
   int g_row_start[B200_MAX_GROUPS + 1];
-  int g_mtile_start[B200_MAX_GROUPS + 1];
+  int g_mtile_start[B200_MAX_GROUPS + 1];   // in 128-row tiles (arrival counters)
+  int g_sched_start[B200_MAX_GROUPS + 1];   // in scheduling tiles (128 rows x CTAs per pair)
+  int total_sched;
   // sender tables (fused dispatch), indexed by rotated bucket number
   int b_count[B200_MAX_EXPERTS];       // rows this rank sends to the bucket
   int b_send_start[B200_MAX_EXPERTS];  // first row of the bucket in send_order
@@ -73,8 +73,19 @@ struct __align__(16) ControlSmem {
   int b_unit_start[B200_MAX_EXPERTS + 1];
 };
 
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + (int)sizeof(ControlSmem) + 1024;
-static_assert(SMEM_BYTES <= 232448, "exceeds 227 KiB of shared memory per CTA");
+// Per-variant geometry.  CG = CTAs cooperating on one MMA (tcgen05 cta_group): with CG == 2
+// the pair computes a 256 x 256 tile, each CTA staging its own 128 rows of A and its own
+// 128 of the 256 weight rows, so a stage is 32 KiB per CTA and six stages fit.
+template <int CG>
+struct Geo {
+  static constexpr int STAGES = CG == 2 ? 6 : 4;
+  static constexpr int B_ROWS = BN / CG;
+  static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
+  static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+  static constexpr int TM = BM * CG;                   // rows of a scheduling tile
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + (int)sizeof(ControlSmem) + 1024;
+  static_assert(SMEM_BYTES <= 232448, "exceeds 227 KiB of shared memory per CTA");
+};
 
 // Maps a linear tile index to (group, m-tile, n-tile).  Tiles are ordered per
 // group in chunks of `gm` M-tiles; inside a chunk the M index runs fastest so
@@ -82,11 +93,11 @@ static_assert(SMEM_BYTES <= 232448, "exceeds 227 KiB of shared memory per CTA");
 // that stays resident in L2 while the N index sweeps.
 __device__ __forceinline__ bool decode_tile(const ControlSmem& c, int G, int TN, int gm, int idx,
                                             int& cursor, int& g, int& m, int& n) {
-  while (cursor < G && idx >= TN * c.g_mtile_start[cursor + 1]) ++cursor;
+  while (cursor < G && idx >= TN * c.g_sched_start[cursor + 1]) ++cursor;
   if (cursor >= G) return false;
   g = cursor;
-  const int tm = c.g_mtile_start[g + 1] - c.g_mtile_start[g];
-  const int j = idx - TN * c.g_mtile_start[g];
+  const int tm = c.g_sched_start[g + 1] - c.g_sched_start[g];
+  const int j = idx - TN * c.g_sched_start[g];
   const int chunk_tiles = gm * TN;
   const int ch = j / chunk_tiles;
   const int r = j - ch * chunk_tiles;
@@ -97,30 +108,36 @@ __device__ __forceinline__ bool decode_tile(const ControlSmem& c, int G, int TN,
 }
 
 // Exclusive scan of g_rows into g_row_start / g_mtile_start by one warp.
-__device__ __forceinline__ void scan_groups(ControlSmem& c, int G, int lane) {
-  int row_carry = 0, tile_carry = 0;
+__device__ __forceinline__ void scan_groups(ControlSmem& c, int G, int lane, int sched_rows) {
+  int row_carry = 0, tile_carry = 0, sched_carry = 0;
   for (int base = 0; base < G; base += 32) {
     const int g = base + lane;
     const int rows = (g < G) ? c.g_rows[g] : 0;
     const int tiles = (rows + BM - 1) / BM;
-    int rs = rows, ts = tiles;
+    const int sched = (rows + sched_rows - 1) / sched_rows;
+    int rs = rows, ts = tiles, ss = sched;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
       const int r2 = __shfl_up_sync(0xffffffffu, rs, o);
       const int t2 = __shfl_up_sync(0xffffffffu, ts, o);
-      if (lane >= o) { rs += r2; ts += t2; }
+      const int s2 = __shfl_up_sync(0xffffffffu, ss, o);
+      if (lane >= o) { rs += r2; ts += t2; ss += s2; }
     }
     if (g < G) {
       c.g_row_start[g] = row_carry + rs - rows;
       c.g_mtile_start[g] = tile_carry + ts - tiles;
+      c.g_sched_start[g] = sched_carry + ss - sched;
     }
     row_carry += __shfl_sync(0xffffffffu, rs, 31);
     tile_carry += __shfl_sync(0xffffffffu, ts, 31);
+    sched_carry += __shfl_sync(0xffffffffu, ss, 31);
   }
   if (lane == 0) {
     c.g_row_start[G] = row_carry;
     c.g_mtile_start[G] = tile_carry;
     c.total_mtiles = tile_carry;
+    c.g_sched_start[G] = sched_carry;
+    c.total_sched = sched_carry;
   }
 }
 
@@ -174,7 +191,7 @@ __device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200
   }
 }
 
-template <int EPI, bool FUSED>
+template <int EPI, bool FUSED, int CG>
 __global__ void __launch_bounds__(FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                     const __grid_constant__ CUtensorMap tmap_b, const b200_gemm_args ga,
@@ -183,6 +200,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
+  using S = Geo<CG>;
+  constexpr int STAGES = S::STAGES;
+  constexpr int STAGE_BYTES = S::STAGE_BYTES;
   uint8_t* stage_base = smem;
   uint8_t* staging = smem + STAGES * STAGE_BYTES;
   ControlSmem& c = *reinterpret_cast<ControlSmem*>(staging + STG_BYTES);
@@ -195,6 +215,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int TN = (ga.N + BN - 1) / BN;
   const int KB = (ga.K + BK - 1) / BK;
   const int gm = ga.group_m > 0 ? ga.group_m : 16;
+  // CTA pair bookkeeping: both CTAs of a pair walk the same tile list; CTA `cta_rank`
+  // owns rows [cta_rank*128, +128) of each 256-row tile and half of the weight rows.
+  const uint32_t cta_rank = (CG == 2) ? cluster_ctarank() : 0u;
+  const int sched_id = blockIdx.x / CG;
+  const int sched_stride = gridDim.x / CG;
 
   WaitCtx w;
   w.abort_flag = &c.abort_flag;
@@ -211,7 +236,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(&c.tmem_full[a], 1);
-      mbar_init(&c.tmem_empty[a], 128);
+      mbar_init(&c.tmem_empty[a], 128 * CG);   // every epilogue thread of the pair arrives
     }
     mbar_init(&c.drain, 1);
     fence_mbar_init();
@@ -219,10 +244,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(&c.tmem_base, TMEM_COLS);
-    tmem_relinquish();
+    if constexpr (CG == 2) {
+      tmem_alloc_pair(&c.tmem_base, TMEM_COLS);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(&c.tmem_base, TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();   // the peer's barriers exist before anyone signals them
 
   if constexpr (FUSED) {
     // every rank's routing counts must have landed before offsets can be built
@@ -249,7 +280,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
   __syncthreads();
-  if (warp == 0) scan_groups(c, G, lane);
+  if (warp == 0) scan_groups(c, G, lane, S::TM);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -263,7 +294,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   }
 
   const uint32_t tmem_base = c.tmem_base;
-  const int total_tiles = c.total_mtiles * TN;
+  const int total_tiles = c.total_sched * TN;
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -272,30 +303,46 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t phase = 0;
       int issued = 0;
       bool ok = !c.abort_flag;
-      for (int idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x) {
+      for (int idx = sched_id; ok && idx < total_tiles; idx += sched_stride) {
         int g, m, n;
         if (!decode_tile(c, G, TN, gm, idx, cursor, g, m, n)) break;
-        const int row0 = c.g_row_start[g] + m * BM;
+        const int half0 = m * S::TM + static_cast<int>(cta_rank) * BM;   // first row of my half
+        const int row0 = c.g_row_start[g] + half0;
         if constexpr (FUSED) {
-          const uint32_t expect = static_cast<uint32_t>(min(BM, c.g_rows[g] - m * BM));
-          const uint32_t* ready = reinterpret_cast<const uint32_t*>(da.peer_ready[da.rank]) +
-                                  c.g_mtile_start[g] + m;
-          if (!wait_flag_geq(ready, expect, w, ST_TIMEOUT_TILE_READY)) { ok = false; break; }
-          fence_proxy_async();   // peer-written rows are read by the async proxy next
+          const int expect = min(BM, c.g_rows[g] - half0);
+          if (expect > 0) {
+            const uint32_t* ready = reinterpret_cast<const uint32_t*>(da.peer_ready[da.rank]) +
+                                    c.g_mtile_start[g] + m * CG + static_cast<int>(cta_rank);
+            if (!wait_flag_geq(ready, static_cast<uint32_t>(expect), w, ST_TIMEOUT_TILE_READY)) {
+              ok = false;
+              break;
+            }
+            fence_proxy_async();   // peer-written rows are read by the async proxy next
+          }
         }
-        const int brow = g * ga.N + n * BN;
+        const int brow = g * ga.N + n * BN + static_cast<int>(cta_rank) * S::B_ROWS;
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&c.empty[stage], phase ^ 1u, w, ST_TIMEOUT_PIPE_EMPTY)) { ok = false; break; }
           uint8_t* sa = stage_base + stage * STAGE_BYTES;
-          mbar_expect_tx(&c.full[stage], STAGE_BYTES);
-          tma_load_2d(sa, &tmap_a, &c.full[stage], kb * BK, row0);
-          tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, &c.full[stage], kb * BK, brow);
+          if constexpr (CG == 2) {
+            // the pair leader's barrier collects the bytes of both CTAs' loads
+            if (cta_rank == 0) mbar_expect_tx(&c.full[stage], STAGE_BYTES * 2);
+            const uint32_t lead_bar = map_to_cta(&c.full[stage], 0);
+            tma_load_2d_pair(sa, &tmap_a, lead_bar, kb * BK, row0);
+            tma_load_2d_pair(sa + A_STAGE_BYTES, &tmap_b, lead_bar, kb * BK, brow);
+          } else {
+            mbar_expect_tx(&c.full[stage], STAGE_BYTES);
+            tma_load_2d(sa, &tmap_a, &c.full[stage], kb * BK, row0);
+            tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, &c.full[stage], kb * BK, brow);
+          }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
-      // Retire every load still in flight before shared memory is released.
-      const int pending = min(issued, STAGES);
+      // Retire every load still in flight before shared memory is released.  In a CTA
+      // pair the leader's barriers account for both CTAs' loads, and the pair leaves
+      // together (cluster barrier at teardown), so only the leader drains.
+      const int pending = (CG == 2 && cta_rank != 0) ? 0 : min(issued, STAGES);
       for (int i = 0; i < pending; ++i) {
         // walk back from the most recent issue
         int s = stage - 1 - i;
@@ -309,13 +356,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc_bf16_f32(BM, ga.mma_n > 0 ? ga.mma_n : BN);
+    if (lane == 0 && cta_rank == 0) {
+      const uint32_t idesc = make_idesc_bf16_f32(S::TM, ga.mma_n > 0 ? ga.mma_n : BN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = !c.abort_flag;
-      for (int idx = blockIdx.x; ok && idx < total_tiles; idx += gridDim.x, ++it) {
+      for (int idx = sched_id; ok && idx < total_tiles; idx += sched_stride, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&c.tmem_empty[acc], acc_phase ^ 1u, w, ST_TIMEOUT_TMEM_EMPTY)) break;
@@ -330,16 +377,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advancing 16 elements along K = 32 bytes = 2 descriptor units
-            umma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            if constexpr (CG == 2)
+              umma_bf16_ss_pair(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            else
+              umma_bf16_ss(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&c.empty[stage]);
+          // frees the stage in both CTAs of a pair
+          if constexpr (CG == 2) umma_commit_pair(&c.empty[stage], 3);
+          else umma_commit(&c.empty[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        umma_commit(&c.tmem_full[acc]);
+        if constexpr (CG == 2) umma_commit_pair(&c.tmem_full[acc], 3);
+        else umma_commit(&c.tmem_full[acc]);
       }
       // all MMAs issued by this thread must retire before TMEM is freed
-      umma_commit(&c.drain);
+      if constexpr (CG == 2) umma_commit_pair(&c.drain, 1);
+      else umma_commit(&c.drain);
       WaitCtx wd = w;
       int no_abort = 0;
       wd.abort_flag = &no_abort;
@@ -353,13 +407,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int row_in_tile = q * 32 + lane;
     uint8_t* my_stg = staging + row_in_tile * STG_ROW_BYTES;
     int cursor = 0, it = 0;
-    for (int idx = blockIdx.x; idx < total_tiles; idx += gridDim.x, ++it) {
+    // accumulators are handed back on the pair leader's barrier
+    const uint32_t tmem_empty_addr[2] = {map_to_cta(&c.tmem_empty[0], 0), map_to_cta(&c.tmem_empty[1], 0)};
+    for (int idx = sched_id; idx < total_tiles; idx += sched_stride, ++it) {
       int g, m, n;
       if (!decode_tile(c, G, TN, gm, idx, cursor, g, m, n)) break;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int rows_in_tile = min(BM, c.g_rows[g] - m * BM);
-      const int row0 = c.g_row_start[g] + m * BM;
+      const int half0 = m * S::TM + static_cast<int>(cta_rank) * BM;
+      const int rows_in_tile = min(BM, c.g_rows[g] - half0);      // may be <= 0 for the upper half
+      const int row0 = c.g_row_start[g] + half0;
       bool valid = row_in_tile < rows_in_tile;
 
       // warp-uniform decision: the TMEM loads below need the whole warp
@@ -424,7 +481,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         tc_fence_before_sync();
-        mbar_arrive(&c.tmem_empty[acc]);
+        if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_addr[acc]);
+          else mbar_arrive(&c.tmem_empty[acc]);
         if (valid) {
           const float inv = 1.0f / sum;
           float p[ROUTER_MAX_K];
@@ -483,7 +541,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (p == PASSES - 1) {
           // every TMEM read of this accumulator is done: hand it back to the MMA warp
           tc_fence_before_sync();
-          mbar_arrive(&c.tmem_empty[acc]);
+          if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_addr[acc]);
+          else mbar_arrive(&c.tmem_empty[acc]);
         }
         __syncwarp();
         // coalesced write-out: 8 lanes cover one 128-byte row segment, 4 rows per step
@@ -578,9 +637,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   // ---------------------------------------------------------------- teardown
   tc_fence_before_sync();
   __syncthreads();
+  if constexpr (CG == 2) cluster_sync_all();   // the leader's MMAs read both CTAs' shared memory
   if (warp == 1) {
     tc_fence_after_sync();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (CG == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -620,19 +681,32 @@ static int make_tmap_bf16(CUtensorMap* tm, const void* base, long long rows, lon
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
-template <int EPI, bool FUSED>
+template <int EPI, bool FUSED, int CG>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const b200_gemm_args& ga,
                           const b200_dispatch_args& da, const b200_combine_args& ca,
                           const b200_router_args& ra, int ctas, cudaStream_t stream) {
   static bool configured = false;
-  auto kern = grouped_gemm_kernel<EPI, FUSED>;
+  auto kern = grouped_gemm_kernel<EPI, FUSED, CG>;
+  constexpr int smem = Geo<CG>::SMEM_BYTES;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  kern<<<ctas, FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, SMEM_BYTES, stream>>>(ta, tb, ga, da, ca, ra);
-  return static_cast<int>(cudaGetLastError());
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(CG == 2 ? (ctas / 2) * 2 : ctas, 1, 1);
+  cfg.blockDim = dim3(FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, tb, ga, da, ca, ra));
 }
 
 }  // namespace b200
@@ -663,7 +737,8 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
   CUtensorMap ta, tb;
   int r = make_tmap_bf16(&ta, a, a_rows, ga->K, BM);
   if (r != 0) return r;
-  r = make_tmap_bf16(&tb, w, static_cast<long long>(G) * ga->N, ga->K, BN);
+  r = make_tmap_bf16(&tb, w, static_cast<long long>(G) * ga->N, ga->K,
+                     (ga->cta_pair != 0 && num_ctas >= 2) ? BN / 2 : BN);
   if (r != 0) return r - 10;
   b200_dispatch_args dz;
   b200_combine_args cz;
@@ -676,23 +751,30 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
   const b200_combine_args& c = ca ? *ca : cz;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (num_ctas <= 0) return -14;
+  const bool pair = ga->cta_pair != 0 && num_ctas >= 2;
   if (!fused) {
     switch (epi) {
-      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, false>(ta, tb, *ga, d, c, r2, num_ctas, st);
-      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, false>(ta, tb, *ga, d, c, r2, num_ctas, st);
-      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, false>(ta, tb, *ga, d, c, r2, num_ctas, st);
-      case B200_EPI_ROUTER: return launch_variant<B200_EPI_ROUTER, false>(ta, tb, *ga, d, c, r2, num_ctas, st);
+      case B200_EPI_STORE: return (pair ? launch_variant<B200_EPI_STORE, false, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_STORE, false, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_SILU_GATE: return (pair ? launch_variant<B200_EPI_SILU_GATE, false, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_SILU_GATE, false, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_COMBINE: return (pair ? launch_variant<B200_EPI_COMBINE, false, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_COMBINE, false, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_ROUTER: return launch_variant<B200_EPI_ROUTER, false, 1>(ta, tb, *ga, d, c, r2, num_ctas, st);
     }
   } else {
     switch (epi) {
-      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, true>(ta, tb, *ga, d, c, r2, num_ctas, st);
-      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, true>(ta, tb, *ga, d, c, r2, num_ctas, st);
-      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, true>(ta, tb, *ga, d, c, r2, num_ctas, st);
+      case B200_EPI_STORE: return (pair ? launch_variant<B200_EPI_STORE, true, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_STORE, true, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_SILU_GATE: return (pair ? launch_variant<B200_EPI_SILU_GATE, true, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_SILU_GATE, true, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_COMBINE: return (pair ? launch_variant<B200_EPI_COMBINE, true, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_COMBINE, true, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
     }
   }
   return -15;
 }
 
-int b200_gemm_smem_bytes() { return b200::SMEM_BYTES; }
+int b200_gemm_smem_bytes() { return b200::Geo<1>::SMEM_BYTES; }
 
 }  // extern "C"

@@ -187,6 +187,10 @@ class MoELayer(nn.Module):
             [C.c_void_p, C.c_void_p, C.c_uint, C.c_int, C.c_int, C.c_int, C.c_void_p,
              C.POINTER(RetireArgs), C.c_void_p, C.c_ulonglong, C.c_void_p])
         self._ctas = sm_count(dev)
+        pair = cfg.cta_pair
+        if pair is None:      # 256-row tiles pay off once an expert sees a few of them
+            pair = (T * k * W) // max(ET, 1) >= 256
+        self._cta_pair = int(bool(pair))
         self._budget_ns = int(cfg.wait_budget_ms * 1e6)
         # every rank's buffers exist and are zeroed before anyone dispatches
         torch.cuda.synchronize(dev)
@@ -282,6 +286,7 @@ class MoELayer(nn.Module):
         ga = nv.GemmArgs()
         ga.num_groups, ga.K, ga.group_m = EL, D, 16
         ga.status, ga.wait_budget_ns = status_p, self._budget_ns
+        ga.cta_pair = self._cta_pair
         recv = self.recv[par]
         if cfg.gated:
             F = cfg.ffn_dim
@@ -296,6 +301,7 @@ class MoELayer(nn.Module):
             gb.num_groups, gb.N, gb.K, gb.n_out, gb.group_m = EL, D, F, D, 16
             gb.group_rows = self.group_rows.data_ptr()
             gb.status, gb.wait_budget_ns = status_p, self._budget_ns
+            gb.cta_pair = self._cta_pair
             nv.check(lib.b200_grouped_gemm(ptr(self.hidden), self.cap_rows, ptr(self.w2), nv.EPI_COMBINE,
                                            0, C.byref(gb), None, C.byref(ca), None, self._ctas, st),
                      "GEMM2+combine launch")

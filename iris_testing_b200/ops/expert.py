@@ -35,12 +35,15 @@ def to_kmajor(weights: torch.Tensor) -> torch.Tensor:
 def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tensor, *,
                  epilogue: int = nv.EPI_STORE, out: Optional[torch.Tensor] = None,
                  status: Optional[torch.Tensor] = None, group_m: int = 16,
-                 num_ctas: Optional[int] = None, wait_budget_ms: float = 2000.0) -> torch.Tensor:
+                 num_ctas: Optional[int] = None, wait_budget_ms: float = 2000.0,
+                 cta_pair: Optional[bool] = None) -> torch.Tensor:
     """out[rows of group g] = a[rows of group g] @ w_kmajor[g].T   (bf16 in, fp32 accumulate).
 
     a          [M, K] bf16, groups packed back to back
     w_kmajor   [G, N, K] bf16
     group_rows int32 [G] on the device (rows per group; sum <= M)
+    cta_pair   True: two CTAs per MMA (tcgen05 cta_group::2, 256-row tiles); None picks it
+               when the groups average at least 256 rows.
     epilogue   EPI_STORE -> out [M, N];  EPI_SILU_GATE -> out [M, N/2] where every
                256-row block of a group's weight holds 128 gate rows then 128 up rows.
     """
@@ -83,6 +86,9 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     ga.out, ga.ldo = out.data_ptr(), n_out
     ga.status = status.data_ptr()
     ga.wait_budget_ns = int(wait_budget_ms * 1e6)
+    if cta_pair is None:
+        cta_pair = M >= 256 * G
+    ga.cta_pair = int(bool(cta_pair))
     ctas = num_ctas or sm_count(a.device)
     rc = nv.lib().b200_grouped_gemm(ptr(a), M, ptr(w_kmajor), epilogue, 0, C.byref(ga), None, None,
                                     None, ctas, stream_ptr(a))

@@ -24,13 +24,14 @@ def _dense(layer, x):
     return cpu_ref.dense_moe_ref(x, layer.router, cfg.topk, w_single=w1, bias=layer.router_bias)
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("D,F,E,k,gated,T", [
     (256, 512, 8, 2, True, 200), (256, 0, 4, 1, False, 77), (2048, 1408, 32, 4, True, 2048),
-    (512, 256, 64, 8, True, 1000), (128, 0, 8, 2, False, 128)])
-def test_fused_layer_matches_dense_reference(D, F, E, k, gated, T):
+    (512, 256, 64, 8, True, 1000), (128, 0, 8, 2, False, 128), (1024, 1024, 2, 2, True, 3000)])
+def test_fused_layer_matches_dense_reference(D, F, E, k, gated, T, pair):
     from iris_testing_b200.config import MoEConfig
     from iris_testing_b200.utils import gen_local_tokens
-    cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=E, topk=k, gated=gated)
+    cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=E, topk=k, gated=gated, cta_pair=pair)
     layer, heap = _make(cfg, T)
     dev = heap.device
     for i in range(3):                                  # exercises both parity slots and re-arming

@@ -70,7 +70,7 @@ def test_plan_and_pack(dev, T, k, E):
     assert torch.equal(pack_rows(x, p.send_order, k), cpu_ref.pack_ref(x, r.send_order, k))
 
 
-def _gemm_case(dev, rows_list, N, K, gated):
+def _gemm_case(dev, rows_list, N, K, gated, pair=False):
     from iris_testing_b200 import _native as nv
     from iris_testing_b200.ops import grouped_gemm
     G, M = len(rows_list), max(sum(rows_list), 1)
@@ -79,7 +79,8 @@ def _gemm_case(dev, rows_list, N, K, gated):
     w = (torch.randn(G, N, K, generator=g) * 0.05).to(dev, torch.bfloat16)
     rows = torch.tensor(rows_list, dtype=torch.int32, device=dev)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
-    out = grouped_gemm(a, w, rows, epilogue=nv.EPI_SILU_GATE if gated else nv.EPI_STORE, status=status)
+    out = grouped_gemm(a, w, rows, epilogue=nv.EPI_SILU_GATE if gated else nv.EPI_STORE, status=status,
+                       cta_pair=pair)
     ref = torch.zeros(M, N, device=dev)
     off = 0
     for gi, r in enumerate(rows_list):
@@ -96,13 +97,15 @@ def _gemm_case(dev, rows_list, N, K, gated):
 @pytest.mark.parametrize("rows,N,K", [([128], 256, 64), ([100], 256, 512), ([300, 0, 77, 129], 512, 512),
                                       ([37] * 16, 2048, 1408), ([5, 200], 136, 72), ([0, 0, 1], 256, 128),
                                       ([4096], 1024, 4096)])
-def test_grouped_gemm_plain(dev, rows, N, K):
-    _gemm_case(dev, rows, N, K, gated=False)
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_gemm_plain(dev, rows, N, K, pair):
+    _gemm_case(dev, rows, N, K, gated=False, pair=pair)
 
 
 @pytest.mark.parametrize("rows,N,K", [([300, 0, 77, 129], 512, 512), ([1000, 513], 2816, 2048)])
-def test_grouped_gemm_silu_gate(dev, rows, N, K):
-    _gemm_case(dev, rows, N, K, gated=True)
+@pytest.mark.parametrize("pair", [False, True])
+def test_grouped_gemm_silu_gate(dev, rows, N, K, pair):
+    _gemm_case(dev, rows, N, K, gated=True, pair=pair)
 
 
 def test_expert_op_reference_signature(dev):
