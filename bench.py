@@ -67,6 +67,16 @@ class ClockSampler:
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+            return
+        # nvidia-smi needs a moment to enumerate the GPUs: wait for its first sample
+        t0 = time.time()
+        while time.time() - t0 < 10.0:
+            try:
+                if os.path.getsize(self.path) > 0:
+                    break
+            except OSError:
+                pass
+            time.sleep(0.05)
 
     def stop(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
@@ -213,7 +223,14 @@ def run_ours(args) -> None:
             bufs[b].copy_(hosts[b], non_blocking=True)
             ready[b].record(copy_stream)
 
+    result_host = torch.zeros(2, dtype=torch.float32).pin_memory()
+    result_ready = [torch.cuda.Event() for _ in range(2)]
+
     def e2e_loop(n: int) -> float:
+        """Every step: H2D of that step's tokens (prefetched on a copy stream, overlapping the
+        previous step's compute), forward, and a D2H read of the step's result scalar.  The
+        scalar of step i is read on the host while step i+1 is already queued, so the GPU
+        never idles waiting for the host."""
         for b in range(2):
             freed[b].record(main)
         fence(world)
@@ -228,7 +245,13 @@ def run_ours(args) -> None:
             main.wait_event(ready[b])
             out = layer(bufs[b])
             freed[b].record(main)
-            acc += float(torch.linalg.vector_norm(out).item())   # D2H read of the step's result
+            result_host[b:b + 1].copy_(torch.linalg.vector_norm(out).reshape(1), non_blocking=True)
+            result_ready[b].record(main)
+            if i > 0:                             # D2H read of the previous step's result
+                result_ready[1 - b].synchronize()
+                acc += float(result_host[1 - b])
+        result_ready[(n - 1) & 1].synchronize()
+        acc += float(result_host[(n - 1) & 1])
         t1.record()
         fence(world)
         return t0.elapsed_time(t1) * 1000.0 / n
@@ -254,7 +277,25 @@ def ensure_reference() -> str | None:
     ref = ROOT / "baseline" / "_ref"
     if (ref / "baseline.py").exists() and (ref / "utils.py").exists():
         return None
-    return "baseline/_ref is missing (reference not installed on this box)"
+    # not shipped with this checkout: install it now if the reference tree is mounted
+    src = Path(os.environ.get("REFERENCE_DIR", "/root/reference"))
+    if int(os.environ.get("RANK", "0")) == 0 and src.exists():
+        sys.path.insert(0, str(ROOT / "baseline"))
+        try:
+            from install_reference import install
+            err = install(src)
+        except Exception as exc:
+            err = repr(exc)[:200]
+        if err is not None:
+            return f"reference install failed: {err}"
+    elif src.exists():                      # other ranks wait for rank 0's install
+        t0 = time.time()
+        while time.time() - t0 < 180 and not (ref / "unit_tests.py").exists():
+            time.sleep(0.5)
+        time.sleep(1.0)
+    if (ref / "baseline.py").exists() and (ref / "utils.py").exists():
+        return None
+    return "baseline/_ref is missing and no reference tree is mounted to install it from"
 
 
 def run_reference(args) -> None:

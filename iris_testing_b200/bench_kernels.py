@@ -117,7 +117,7 @@ def main() -> None:
     g = sub.add_parser("gemm")
     g.add_argument("--groups", type=int, default=4); g.add_argument("--rows", type=int, default=4096)
     g.add_argument("--n", type=int, default=2048); g.add_argument("--k", type=int, default=4096)
-    g.add_argument("--gated", type=int, default=0); g.add_argument("--group-m", dest="group_m", type=int, default=16)
+    g.add_argument("--gated", type=int, default=0); g.add_argument("--group-m", dest="group_m", type=int, default=0)
     r = sub.add_parser("router")
     r.add_argument("--tokens", type=int, default=16384); r.add_argument("--hidden", type=int, default=4096)
     r.add_argument("--experts", type=int, default=8); r.add_argument("--topk", type=int, default=2)

@@ -23,6 +23,21 @@ struct PeerTable {
   unsigned long long p[B200_MAX_WORLD];
 };
 
+// One warp copies a row of `row16` 16-byte chunks with up to eight loads in flight per lane
+// (a remote store costs microseconds of latency; the copy is throughput- not latency-bound
+// only with enough independent accesses outstanding).
+__device__ __forceinline__ void copy_row_16(uint4* dst, const uint4* src, int row16, int lane) {
+  for (int i = lane; i < row16; i += 256) {
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (i + 32 * j < row16) v[j] = ld_16(src + i + 32 * j);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (i + 32 * j < row16) st_16(dst + i + 32 * j, v[j]);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Padded dispatch.  Layouts (identical to the reference's data contract):
 //   send_payload [sum_send, H]  rows ordered by destination, then local expert
@@ -68,7 +83,7 @@ __global__ void padded_dispatch_kernel(const uint4* __restrict__ payload,
   for (int r = warp; r < rows; r += nwarps) {
     const uint4* s = payload + (src_row0 + r) * row16;
     uint4* d = tb + (dst_row0 + r) * row16;
-    for (int i = lane; i < row16; i += 32) st_16(d + i, ld_nc_16(s + i));
+    copy_row_16(d, s, row16, lane);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -100,7 +115,7 @@ __global__ void padded_return_kernel(const uint4* __restrict__ out_buf, const in
   for (int r = warp; r < rows; r += nwarps) {
     const uint4* s = out_buf + (in_row0 + r) * row16;
     uint4* d = rb + (out_row0 + r) * row16;
-    for (int i = lane; i < row16; i += 32) st_16(d + i, ld_16(s + i));
+    copy_row_16(d, s, row16, lane);
   }
   __syncthreads();
   if (threadIdx.x == 0) {

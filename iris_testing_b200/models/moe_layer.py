@@ -284,7 +284,7 @@ class MoELayer(nn.Module):
         ca.peer_arrived = heap.peer_ptrs(self.arrived)
 
         ga = nv.GemmArgs()
-        ga.num_groups, ga.K, ga.group_m = EL, D, 16
+        ga.num_groups, ga.K, ga.group_m = EL, D, 0
         ga.status, ga.wait_budget_ns = status_p, self._budget_ns
         ga.cta_pair = self._cta_pair
         recv = self.recv[par]
@@ -298,7 +298,7 @@ class MoELayer(nn.Module):
             ev("dispatch+gemm1")
             # 4. GEMM2 + combine (one kernel)
             gb = nv.GemmArgs()
-            gb.num_groups, gb.N, gb.K, gb.n_out, gb.group_m = EL, D, F, D, 16
+            gb.num_groups, gb.N, gb.K, gb.n_out, gb.group_m = EL, D, F, D, 0
             gb.group_rows = self.group_rows.data_ptr()
             gb.status, gb.wait_budget_ns = status_p, self._budget_ns
             gb.cta_pair = self._cta_pair

@@ -34,7 +34,7 @@ def to_kmajor(weights: torch.Tensor) -> torch.Tensor:
 
 def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tensor, *,
                  epilogue: int = nv.EPI_STORE, out: Optional[torch.Tensor] = None,
-                 status: Optional[torch.Tensor] = None, group_m: int = 16,
+                 status: Optional[torch.Tensor] = None, group_m: int = 0,
                  num_ctas: Optional[int] = None, wait_budget_ms: float = 2000.0,
                  cta_pair: Optional[bool] = None) -> torch.Tensor:
     """out[rows of group g] = a[rows of group g] @ w_kmajor[g].T   (bf16 in, fp32 accumulate).
@@ -42,6 +42,7 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     a          [M, K] bf16, groups packed back to back
     w_kmajor   [G, N, K] bf16
     group_rows int32 [G] on the device (rows per group; sum <= M)
+    group_m    M-tiles per L2-blocking chunk; 0 picks about 24 MB of activations per chunk.
     cta_pair   True: two CTAs per MMA (tcgen05 cta_group::2, 256-row tiles); None picks it
                when the groups average at least 256 rows.
     epilogue   EPI_STORE -> out [M, N];  EPI_SILU_GATE -> out [M, N/2] where every
