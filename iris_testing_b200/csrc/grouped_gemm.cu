@@ -407,6 +407,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int row_in_tile = q * 32 + lane;
     uint8_t* my_stg = staging + row_in_tile * STG_ROW_BYTES;
     int cursor = 0, it = 0;
+    int pending_arrivals = 0;   // combine epilogue: rows stored for rank `lane`, not yet published
     // accumulators are handed back on the pair leader's barrier
     const uint32_t tmem_empty_addr[2] = {map_to_cta(&c.tmem_empty[0], 0), map_to_cta(&c.tmem_empty[1], 0)};
     for (int idx = sched_id; idx < total_tiles; idx += sched_stride, ++it) {
@@ -562,13 +563,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
 
       if constexpr (EPI == B200_EPI_COMBINE) {
-        // one arrival count per (row, n-tile), summed per destination rank
+        // One arrival count per (row, n-tile).  The receiver only acts on the grand total,
+        // so the counts are kept per destination rank (lane r of the warp keeps rank r's)
+        // and published once, after this warp's last tile: a system-scope fence per tile
+        // would stall the epilogue longer than a short-K tile takes to compute.
         const unsigned grp = __match_any_sync(0xffffffffu, dst_rank);
-        if (dst_rank >= 0 && lane == (__ffs(grp) - 1)) {
-          fence_acq_rel_sys();
-          red_add_release_sys(reinterpret_cast<uint32_t*>(ca.peer_arrived[dst_rank]),
-                              static_cast<uint32_t>(__popc(grp)));
+        const int leader_cnt = (dst_rank >= 0 && lane == (__ffs(grp) - 1)) ? __popc(grp) : 0;
+#pragma unroll
+        for (int r = 0; r < B200_MAX_WORLD; ++r) {
+          // sum over the (at most one per group) leaders whose destination is rank r
+          const unsigned m = __ballot_sync(0xffffffffu, leader_cnt > 0 && dst_rank == r);
+          if (m != 0u) {
+            const int c2 = __shfl_sync(0xffffffffu, leader_cnt, __ffs(m) - 1);
+            if (lane == r) pending_arrivals += c2;
+          }
         }
+      }
+    }
+    if constexpr (EPI == B200_EPI_COMBINE) {
+      __syncwarp();
+      if (lane < ca.world && pending_arrivals > 0) {
+        fence_acq_rel_sys();
+        red_add_release_sys(reinterpret_cast<uint32_t*>(ca.peer_arrived[lane]),
+                            static_cast<uint32_t>(pending_arrivals));
       }
     }
   } else {

@@ -98,30 +98,41 @@ __global__ void router_topk_simple_kernel(const __nv_bfloat16* __restrict__ x,
 // ---------------------------------------------------------------------------
 __global__ void plan_rank_kernel(const int* __restrict__ topk_idx, int n_flat, int num_experts,
                                  int* __restrict__ rank_in_bucket, int* __restrict__ counts) {
-  __shared__ int warp_cnt[32];
-  __shared__ int carry;
+  // Each warp owns one contiguous segment of the list: pass 1 counts its hits, a scan over
+  // the warp totals gives every segment its base rank, pass 2 hands out the ranks.  Only
+  // two block-wide barriers, whatever the list length.
+  __shared__ int warp_base[33];
   const int e = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  if (threadIdx.x == 0) carry = 0;
+  const int seg = ((n_flat + nwarps - 1) / nwarps + 31) & ~31;
+  const int lo = min(warp * seg, n_flat), hi = min(lo + seg, n_flat);
+  int cnt = 0;
+  for (int i = lo + lane; i < hi; i += 32) cnt += (topk_idx[i] == e) ? 1 : 0;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if (lane == 0) warp_base[warp + 1] = cnt;
   __syncthreads();
-  for (int base = 0; base < n_flat; base += blockDim.x) {
-    const int i = base + threadIdx.x;
-    const bool hit = (i < n_flat) && (topk_idx[i] == e);
-    const unsigned b = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) warp_cnt[warp] = __popc(b);
-    __syncthreads();
-    int before = carry;
-    for (int w2 = 0; w2 < warp; ++w2) before += warp_cnt[w2];
-    if (hit) rank_in_bucket[i] = before + __popc(b & ((1u << lane) - 1u));
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int tot = 0;
-      for (int w2 = 0; w2 < nwarps; ++w2) tot += warp_cnt[w2];
-      carry += tot;
+  if (warp == 0) {
+    int v = (lane < nwarps) ? warp_base[lane + 1] : 0;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
     }
-    __syncthreads();
+    if (lane < nwarps) warp_base[lane + 1] = incl;   // inclusive: base of warp w is warp_base[w]
+    if (lane == 0) warp_base[0] = 0;
   }
-  if (threadIdx.x == 0) counts[e] = carry;
+  __syncthreads();
+  int running = warp_base[warp];
+  for (int base = lo; base < hi; base += 32) {
+    const int i = base + lane;
+    const bool hit = (i < hi) && (topk_idx[i] == e);
+    const unsigned b = __ballot_sync(0xffffffffu, hit);
+    if (hit) rank_in_bucket[i] = running + __popc(b & ((1u << lane) - 1u));
+    running += __popc(b);
+  }
+  if (threadIdx.x == 0) counts[e] = warp_base[nwarps];
   (void)num_experts;
 }
 
