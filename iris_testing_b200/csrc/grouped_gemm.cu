@@ -47,6 +47,7 @@ constexpr int STG_BYTES = BM * STG_ROW_BYTES;         // 18 KiB
 constexpr int TMEM_COLS = 512;                        // two 256-column accumulators
 constexpr int NUM_THREADS_PLAIN = 192;
 constexpr int NUM_THREADS_FUSED = 320;
+constexpr int SEND_ROWS = 32;   // rows per sender work unit (aligned in the destination expert's row space)
 
 struct __align__(16) ControlSmem {
   uint64_t full[MAX_STAGES];
@@ -71,6 +72,7 @@ struct __align__(16) ControlSmem {
   int b_dst_mtile0[B200_MAX_EXPERTS];  // index of the expert's first M-tile at the peer
   int b_dst_rank[B200_MAX_EXPERTS];
   int b_unit_start[B200_MAX_EXPERTS + 1];
+  int ready_seen[64];                  // producer's direct-mapped cache of complete M-tiles
 };
 
 // Per-variant geometry.  CG = CTAs cooperating on one MMA (tcgen05 cta_group): with CG == 2
@@ -182,8 +184,8 @@ __device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200
     c.b_dst_rel0[bi] = within;
     c.b_dst_mtile0[bi] = mtile0;
     c.b_dst_rank[bi] = dst;
-    // units are (bucket, destination M-tile) pairs; stored un-scanned for now
-    c.b_unit_start[bi + 1] = (n > 0) ? ((within + n - 1) / BM - within / BM + 1) : 0;
+    // units are (bucket, aligned block of SEND_ROWS destination rows); stored un-scanned for now
+    c.b_unit_start[bi + 1] = (n > 0) ? ((within + n - 1) / SEND_ROWS - within / SEND_ROWS + 1) : 0;
     if (n > 0 && (group_start + within + n > d.cap_rows || n < 0)) {
       report_status(w.status, ST_OVERFLOW);
       *w.abort_flag = 1;
@@ -230,6 +232,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (tid == 0) {
     c.abort_flag = 0;
     c.total_units = 0;
+    for (int i = 0; i < 64; ++i) c.ready_seen[i] = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&c.full[s], 1);
       mbar_init(&c.empty[s], 1);
@@ -310,14 +313,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int row0 = c.g_row_start[g] + half0;
         if constexpr (FUSED) {
           const int expect = min(BM, c.g_rows[g] - half0);
-          if (expect > 0) {
-            const uint32_t* ready = reinterpret_cast<const uint32_t*>(da.peer_ready[da.rank]) +
-                                    c.g_mtile_start[g] + m * CG + static_cast<int>(cta_rank);
+          const int mt = c.g_mtile_start[g] + m * CG + static_cast<int>(cta_rank);
+          // the same M-tile comes back once per N-tile: poll its counter only the first time
+          if (expect > 0 && c.ready_seen[mt & 63] != mt + 1) {
+            const uint32_t* ready = reinterpret_cast<const uint32_t*>(da.peer_ready[da.rank]) + mt;
             if (!wait_flag_geq(ready, static_cast<uint32_t>(expect), w, ST_TIMEOUT_TILE_READY)) {
               ok = false;
               break;
             }
             fence_proxy_async();   // peer-written rows are read by the async proxy next
+            c.ready_seen[mt & 63] = mt + 1;
           }
         }
         const int brow = g * ga.N + n * BN + static_cast<int>(cta_rank) * S::B_ROWS;
@@ -605,9 +610,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const int j = u - c.b_unit_start[bcur];
         const int rel0 = c.b_dst_rel0[bcur];
         const int nrows = c.b_count[bcur];
-        const int tile = rel0 / BM + j;          // M-tile inside the destination expert
-        const int p_lo = max(0, tile * BM - rel0);
-        const int p_hi = min(nrows, (tile + 1) * BM - rel0);
+        const int blk = rel0 / SEND_ROWS + j;    // aligned row block inside the destination expert
+        const int tile = blk / (BM / SEND_ROWS); // the 128-row M-tile whose counter it feeds
+        const int p_lo = max(0, blk * SEND_ROWS - rel0);
+        const int p_hi = min(nrows, (blk + 1) * SEND_ROWS - rel0);
         const int dst = c.b_dst_rank[bcur];
         const int send0 = c.b_send_start[bcur];
         const int drow0 = c.b_dst_row[bcur];
