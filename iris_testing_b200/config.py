@@ -74,6 +74,8 @@ PRESETS = {
     "fine-grained": dict(hidden_dim=2048, ffn_dim=1408, num_experts=64, topk=8, gated=True),
     # Large experts with skewed routing.
     "large": dict(hidden_dim=6144, ffn_dim=16384, num_experts=8, topk=2, gated=True),
+    # Two Mixtral-sized experts: same tiles as the flagship, small enough for a profiler capture.
+    "mixtral-2e": dict(hidden_dim=4096, ffn_dim=14336, num_experts=2, topk=2, gated=True),
     # Small shape for smoke tests.
     "tiny": dict(hidden_dim=256, ffn_dim=512, num_experts=8, topk=2, gated=True),
 }

@@ -57,7 +57,9 @@ __global__ void padded_dispatch_kernel(const uint4* __restrict__ payload,
                                        PeerTable peer_token_buf, PeerTable peer_counts_ready,
                                        PeerTable peer_token_sync, int rank, int world, int e_local,
                                        int cap, int row16, int block_m, int* status) {
-  const int dst = blockIdx.z, e = blockIdx.y, mt = blockIdx.x;
+  // Destinations are visited in rank-rotated order (this rank first, then rank+1, ...):
+  // at any moment the ranks target different peers instead of all flooding rank 0's links.
+  const int dst = (rank + static_cast<int>(blockIdx.z)) % world, e = blockIdx.y, mt = blockIdx.x;
   if (mt == 0 && e == 0) {
     int* pca = reinterpret_cast<int*>(peer_pca.p[dst]);
     for (int e2 = threadIdx.x; e2 < e_local; e2 += blockDim.x)
@@ -103,7 +105,7 @@ __global__ void padded_dispatch_kernel(const uint4* __restrict__ payload,
 __global__ void padded_return_kernel(const uint4* __restrict__ out_buf, const int* __restrict__ pca,
                                      PeerTable peer_ret_buf, PeerTable peer_ret_sync, int rank,
                                      int world, int e_local, int cap, int row16, int block_m) {
-  const int src = blockIdx.z, e = blockIdx.y, mt = blockIdx.x;
+  const int src = (rank + static_cast<int>(blockIdx.z)) % world, e = blockIdx.y, mt = blockIdx.x;   // rank-rotated
   const int n = min(pca[e * world + src], cap);
   const int m0 = mt * block_m;
   if (m0 >= n) return;
