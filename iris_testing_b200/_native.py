@@ -60,6 +60,8 @@ class DispatchArgs(C.Structure):
         ("peer_meta", C.c_ulonglong * MAX_WORLD),
         ("peer_ready", C.c_ulonglong * MAX_WORLD),
         ("group_rows_out", C.c_void_p),
+        ("trace", C.c_void_p),
+        ("trace_tiles", C.c_int),
     ]
 
 

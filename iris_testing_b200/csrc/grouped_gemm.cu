@@ -259,6 +259,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if constexpr (CG == 2) cluster_sync_all();   // the peer's barriers exist before anyone signals them
 
   if constexpr (FUSED) {
+    if (da.trace != nullptr && blockIdx.x == 0 && tid == 0) da.trace[0] = globaltimer_ns();
     // every rank's routing counts must have landed before offsets can be built
     if (tid < da.world) wait_flag_geq(da.counts_flag + tid, da.epoch, w, ST_TIMEOUT_COUNTS);
     __syncthreads();
@@ -317,12 +318,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // the same M-tile comes back once per N-tile: poll its counter only the first time
           if (expect > 0 && c.ready_seen[mt & 63] != mt + 1) {
             const uint32_t* ready = reinterpret_cast<const uint32_t*>(da.peer_ready[da.rank]) + mt;
+            const uint64_t t_wait = da.trace != nullptr ? globaltimer_ns() : 0ull;
             if (!wait_flag_geq(ready, static_cast<uint32_t>(expect), w, ST_TIMEOUT_TILE_READY)) {
               ok = false;
               break;
             }
             fence_proxy_async();   // peer-written rows are read by the async proxy next
             c.ready_seen[mt & 63] = mt + 1;
+            if (da.trace != nullptr) {   // overlap analysis: when did this tile become usable
+              const uint64_t t_now = globaltimer_ns();
+              if (mt < da.trace_tiles) atomicCAS(da.trace + 2 + mt, 0ull, t_now);   // first observer wins
+              atomicAdd(da.trace + 1, t_now - t_wait);
+            }
           }
         }
         const int brow = g * ga.N + n * BN + static_cast<int>(cta_rank) * S::B_ROWS;
@@ -652,6 +659,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           red_add_release_sys(reinterpret_cast<uint32_t*>(da.peer_ready[dst]) +
                                   c.b_dst_mtile0[bcur] + tile,
                               static_cast<uint32_t>(p_hi - p_lo));
+          if (da.trace != nullptr && dst == da.rank && c.b_dst_mtile0[bcur] + tile < da.trace_tiles)
+            da.trace[2 + da.trace_tiles + c.b_dst_mtile0[bcur] + tile] = globaltimer_ns();
         }
       }
     }

@@ -38,6 +38,10 @@ typedef struct {
   unsigned long long peer_meta[B200_MAX_WORLD];   // uint2 [cap_rows]: {src<<24|slot, weight}
   unsigned long long peer_ready[B200_MAX_WORLD];  // uint32 [cap_mtiles] rows landed per M-tile
   int* group_rows_out;            // [e_local] rows per local expert (for the second GEMM)
+  unsigned long long* trace;      // optional [2 + 2*trace_tiles]: [0] kernel start (ns), [1] summed producer
+                                  // stall (ns), [2 + t] time M-tile t was first seen complete,
+                                  // [2 + trace_tiles + t] time this rank last published rows of its own tile t
+  int trace_tiles;
 } b200_dispatch_args;
 
 // Combine side (epilogue of the second grouped GEMM).

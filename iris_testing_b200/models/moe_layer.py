@@ -25,6 +25,7 @@ process group is up), which is what the plumbing tests use.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -40,6 +41,7 @@ from ..ops.plan import Plan, PlanPushArgs, make_plan
 from ..ops.router import router_topk
 from ..utils import gen
 
+_NVTX = os.getenv("B200MOE_NVTX", "0") == "1"   # NVTX range around every forward
 BM = 128          # rows per GEMM tile
 BN = 256          # weight rows per GEMM tile
 
@@ -121,6 +123,8 @@ class MoELayer(nn.Module):
         self.drop_signal = False        # fault-injection aid for the timeout test
         self.profile = False            # record CUDA events between the phases of forward()
         self.phase_events = []
+        self.trace_arrivals = False     # record when each received M-tile became usable (fused kernel)
+        self._trace = None
         if device.type == "cuda":
             if heap is None:
                 raise ValueError("a SymmetricHeap is required on CUDA")
@@ -215,6 +219,12 @@ class MoELayer(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if not x.is_cuda:
             return self._forward_cpu(x)
+        if _NVTX:
+            torch.cuda.nvtx.range_push("MoELayer.forward")
+            try:
+                return self._forward_fused(x)
+            finally:
+                torch.cuda.nvtx.range_pop()
         return self._forward_fused(x)
 
     def route(self, x: torch.Tensor):
@@ -274,6 +284,12 @@ class MoELayer(nn.Module):
         da.peer_meta = heap.peer_ptrs(self.meta[par])
         da.peer_ready = heap.peer_ptrs(self.ready[par])
         da.group_rows_out = self.group_rows.data_ptr()
+        if self.trace_arrivals:
+            if self._trace is None:
+                self._trace = torch.zeros(2 + 2 * self.cap_mtiles, dtype=torch.int64, device=x.device)
+            self._trace.zero_()
+            da.trace = self._trace.data_ptr()
+            da.trace_tiles = self.cap_mtiles
 
         ca = nv.CombineArgs()
         ca.world = W
@@ -331,6 +347,30 @@ class MoELayer(nn.Module):
         self._iteration = it + 1
         self.last_routing = (idx, wgt)
         return y
+
+    def arrival_report(self) -> dict:
+        """Overlap evidence from the last forward run with ``trace_arrivals = True``: when (relative
+        to the fused kernel's start) the received M-tiles became usable, and how long the TMA
+        producers stalled waiting for rows (summed over CTAs).  Synchronises."""
+        if self._trace is None:
+            raise RuntimeError("set layer.trace_arrivals = True before the forward pass")
+        torch.cuda.synchronize()
+        t = self._trace.cpu()
+        start = int(t[0])
+        seen_all = t[2:2 + self.cap_mtiles]
+        seen = seen_all[seen_all > 0] - start
+        if seen.numel() == 0:
+            return dict(tiles=0)
+        s = torch.sort(seen.double()).values / 1e3
+        pick = lambda q: float(s[min(int(q * (s.numel() - 1)), s.numel() - 1)])
+        sent_all = t[2 + self.cap_mtiles:]
+        sent = torch.sort((sent_all[sent_all > 0] - start).double()).values / 1e3
+        extra = {}
+        if sent.numel():
+            extra = dict(own_first_published_us=float(sent[0]), own_last_published_us=float(sent[-1]))
+        return dict(tiles=int(s.numel()), **extra, first_us=float(s[0]), p50_us=pick(0.5), p90_us=pick(0.9),
+                    last_us=float(s[-1]), producer_stall_us_sum=float(t[1]) / 1e3,
+                    producer_stall_us_per_cta=float(t[1]) / 1e3 / max(self._ctas, 1))
 
     def _mark(self, name: str) -> None:
         e = torch.cuda.Event(enable_timing=True)
