@@ -53,7 +53,7 @@ def install(reference: Path) -> str | None:
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else HERE.parent.parent / "reference"
     err = install(ref)
     print("ok" if err is None else f"failed: {err}")
     sys.exit(0 if err is None else 1)

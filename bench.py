@@ -278,7 +278,8 @@ def ensure_reference() -> str | None:
     if (ref / "baseline.py").exists() and (ref / "utils.py").exists():
         return None
     # not shipped with this checkout: install it now if the reference tree is mounted
-    src = Path(os.environ.get("REFERENCE_DIR", "/root/reference"))
+    # REFERENCE_DIR, or a "reference" directory next to this repository
+    src = Path(os.environ.get("REFERENCE_DIR", str(ROOT.parent / "reference")))
     if int(os.environ.get("RANK", "0")) == 0 and src.exists():
         sys.path.insert(0, str(ROOT / "baseline"))
         try:

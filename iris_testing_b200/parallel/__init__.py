@@ -1,7 +1,8 @@
 """Process-level plumbing: symmetric heap over NVLink peer memory, the CPU/gloo
 backend, and the library all-to-all baseline."""
 from .baseline_nccl import (AllToAllMoEBaseline, ExchangeBuffers, exchange_counts,
-                            exchange_payload, relayout_to_token_buf, run_baseline)
+                            exchange_payload, init_baseline_buffers, relayout_to_token_buf,
+                            run_baseline)
 from .gloo_moe import moe_forward_gloo, padded_exchange, pair_message_rows
 
 

@@ -34,6 +34,17 @@ class ExchangeBuffers:
     out_splits: List[int] = field(default_factory=list)
 
 
+def init_baseline_buffers(world_size: int, e_local: int, capacity: int, hidden_dim: int,
+                          token_dtype: torch.dtype, device, total_recv: int,
+                          allocate_token_buf: bool = False) -> ExchangeBuffers:
+    """Persistent buffers allocated once outside the timing loop (cf. baseline.py:44-74)."""
+    return ExchangeBuffers(
+        recv_counts=torch.empty((world_size, e_local), dtype=torch.int32, device=device),
+        recv_payload=torch.empty((total_recv, hidden_dim), dtype=token_dtype, device=device),
+        token_buf=(torch.empty((e_local, world_size, capacity, hidden_dim), dtype=token_dtype, device=device)
+                   if allocate_token_buf else None))
+
+
 def _world(group=None) -> int:
     return dist.get_world_size(group) if dist.is_initialized() else 1
 
