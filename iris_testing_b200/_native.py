@@ -60,6 +60,12 @@ class DispatchArgs(C.Structure):
         ("peer_meta", C.c_ulonglong * MAX_WORLD),
         ("peer_ready", C.c_ulonglong * MAX_WORLD),
         ("group_rows_out", C.c_void_p),
+        ("iter_ptr", C.c_void_p),
+        ("stride_counts", C.c_ulonglong),
+        ("stride_flag", C.c_ulonglong),
+        ("stride_recv", C.c_ulonglong),
+        ("stride_meta", C.c_ulonglong),
+        ("stride_ready", C.c_ulonglong),
         ("trace", C.c_void_p),
         ("trace_tiles", C.c_int),
     ]
@@ -73,6 +79,8 @@ class CombineArgs(C.Structure):
         ("max_slots", C.c_int),
         ("peer_out", C.c_ulonglong * MAX_WORLD),
         ("peer_arrived", C.c_ulonglong * MAX_WORLD),
+        ("iter_ptr", C.c_void_p),
+        ("stride_meta", C.c_ulonglong),
     ]
 
 

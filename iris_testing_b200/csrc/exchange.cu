@@ -247,6 +247,10 @@ struct RetireArgs {
   uint32_t* ready_counters;          // this parity's tile-ready counters (local)
   int num_ready;
   unsigned int* ticket;              // local scratch counter (zero between launches)
+  // Device-side iteration state: when iter_ptr is set, it = *iter_ptr; the counters of
+  // parity (it & 1) are re-armed, iter_done is published as it + 1 and *iter_ptr becomes it + 1.
+  uint32_t* iter_ptr;
+  unsigned long long stride_ready;   // bytes between the two parity copies of ready_counters
 };
 
 __global__ void slot_reduce_kernel(const __nv_bfloat16* out_slots, uint32_t* arrived,
@@ -295,13 +299,24 @@ __global__ void slot_reduce_kernel(const __nv_bfloat16* out_slots, uint32_t* arr
   }
   __syncthreads();
   if (s_last) {
-    for (int i = threadIdx.x; i < ra.num_ready; i += blockDim.x) ra.ready_counters[i] = 0u;
-    if (threadIdx.x == 0) { *arrived = 0u; *ra.ticket = 0u; }
+    uint32_t done_value = ra.iter_done_value;
+    uint32_t* ready = ra.ready_counters;
+    if (ra.iter_ptr != nullptr) {
+      const uint32_t it = __ldcg(ra.iter_ptr);
+      done_value = it + 1u;
+      if (it & 1u) ready = reinterpret_cast<uint32_t*>(reinterpret_cast<char*>(ready) + ra.stride_ready);
+    }
+    for (int i = threadIdx.x; i < ra.num_ready; i += blockDim.x) ready[i] = 0u;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      *arrived = 0u;
+      *ra.ticket = 0u;
+      if (ra.iter_ptr != nullptr) *ra.iter_ptr = done_value;   // the next iteration's kernels read this
+    }
     __syncthreads();
     if (threadIdx.x < ra.world) {
       fence_acq_rel_sys();
-      st_release_sys(reinterpret_cast<uint32_t*>(ra.peer_iter_done[threadIdx.x]) + ra.rank,
-                     ra.iter_done_value);
+      st_release_sys(reinterpret_cast<uint32_t*>(ra.peer_iter_done[threadIdx.x]) + ra.rank, done_value);
     }
   }
 }

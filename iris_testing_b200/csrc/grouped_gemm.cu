@@ -195,10 +195,38 @@ __device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200
 
 template <int EPI, bool FUSED, int CG>
 __global__ void __launch_bounds__(FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
+                    const __grid_constant__ CUtensorMap tmap_a1,
                     const __grid_constant__ CUtensorMap tmap_b, const b200_gemm_args ga,
-                    const b200_dispatch_args da, const b200_combine_args ca,
+                    const b200_dispatch_args da_in, const b200_combine_args ca_in,
                     const b200_router_args ra) {
+  // Per-parity state: the iteration number lives in device memory (when iter_ptr is set), so
+  // the same launch arguments serve every iteration and a captured graph can be replayed.
+  b200_dispatch_args da = da_in;
+  b200_combine_args ca = ca_in;
+  uint32_t parity = 0;
+  if constexpr (FUSED) {
+    if (da.iter_ptr != nullptr) {
+      const uint32_t it = __ldcg(da.iter_ptr);
+      parity = it & 1u;
+      da.epoch = it + 1u;
+      if (parity) {
+        da.counts_all = reinterpret_cast<const int*>(reinterpret_cast<const char*>(da.counts_all) + da.stride_counts);
+        da.counts_flag = reinterpret_cast<const uint32_t*>(reinterpret_cast<const char*>(da.counts_flag) + da.stride_flag);
+#pragma unroll
+        for (int r = 0; r < B200_MAX_WORLD; ++r) {
+          da.peer_recv[r] += da.stride_recv;
+          da.peer_meta[r] += da.stride_meta;
+          da.peer_ready[r] += da.stride_ready;
+        }
+      }
+    }
+  }
+  if constexpr (EPI == B200_EPI_COMBINE) {
+    if (ca.iter_ptr != nullptr && (__ldcg(ca.iter_ptr) & 1u))
+      ca.row_meta = reinterpret_cast<const char*>(ca.row_meta) + ca.stride_meta;
+  }
+  const CUtensorMap& tmap_a = (FUSED && parity) ? tmap_a1 : tmap_a0;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -714,7 +742,8 @@ static int make_tmap_bf16(CUtensorMap* tm, const void* base, long long rows, lon
 }
 
 template <int EPI, bool FUSED, int CG>
-static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const b200_gemm_args& ga,
+static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta1, const CUtensorMap& tb,
+                          const b200_gemm_args& ga,
                           const b200_dispatch_args& da, const b200_combine_args& ca,
                           const b200_router_args& ra, int ctas, cudaStream_t stream) {
   static bool configured = false;
@@ -738,7 +767,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& tb, const b2
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, tb, ga, da, ca, ra));
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, ta1, tb, ga, da, ca, ra));
 }
 
 }  // namespace b200
@@ -766,8 +795,14 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
                                  ra->topk < 1 || ra->topk > ROUTER_MAX_K || ra->topk > ra->num_experts))
     return -16;
   if (ga->mma_n != 0 && (ga->mma_n % 16 != 0 || ga->mma_n < 16 || ga->mma_n > BN)) return -17;
-  CUtensorMap ta, tb;
+  CUtensorMap ta, ta1, tb;
   int r = make_tmap_bf16(&ta, a, a_rows, ga->K, BM);
+  if (r != 0) return r;
+  // second parity copy of the receive buffer (fused build with device-side iteration state)
+  const void* a1 = (fused && da != nullptr && da->iter_ptr != nullptr)
+                       ? static_cast<const void*>(static_cast<const char*>(a) + da->stride_recv)
+                       : a;
+  r = make_tmap_bf16(&ta1, a1, a_rows, ga->K, BM);
   if (r != 0) return r;
   r = make_tmap_bf16(&tb, w, static_cast<long long>(G) * ga->N, ga->K,
                      (ga->cta_pair != 0 && num_ctas >= 2) ? BN / 2 : BN);
@@ -797,22 +832,22 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
   ga = &ga_auto;
   if (!fused) {
     switch (epi) {
-      case B200_EPI_STORE: return (pair ? launch_variant<B200_EPI_STORE, false, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_STORE, false, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_SILU_GATE: return (pair ? launch_variant<B200_EPI_SILU_GATE, false, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_SILU_GATE, false, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_COMBINE: return (pair ? launch_variant<B200_EPI_COMBINE, false, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_COMBINE, false, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_ROUTER: return launch_variant<B200_EPI_ROUTER, false, 1>(ta, tb, *ga, d, c, r2, num_ctas, st);
+      case B200_EPI_STORE: return (pair ? launch_variant<B200_EPI_STORE, false, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_STORE, false, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_SILU_GATE: return (pair ? launch_variant<B200_EPI_SILU_GATE, false, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_SILU_GATE, false, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_COMBINE: return (pair ? launch_variant<B200_EPI_COMBINE, false, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_COMBINE, false, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_ROUTER: return launch_variant<B200_EPI_ROUTER, false, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st);
     }
   } else {
     switch (epi) {
-      case B200_EPI_STORE: return (pair ? launch_variant<B200_EPI_STORE, true, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_STORE, true, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_SILU_GATE: return (pair ? launch_variant<B200_EPI_SILU_GATE, true, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_SILU_GATE, true, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_COMBINE: return (pair ? launch_variant<B200_EPI_COMBINE, true, 2>(ta, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_COMBINE, true, 1>(ta, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_STORE: return (pair ? launch_variant<B200_EPI_STORE, true, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_STORE, true, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_SILU_GATE: return (pair ? launch_variant<B200_EPI_SILU_GATE, true, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_SILU_GATE, true, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
+      case B200_EPI_COMBINE: return (pair ? launch_variant<B200_EPI_COMBINE, true, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
+                  : launch_variant<B200_EPI_COMBINE, true, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
     }
   }
   return -15;

@@ -38,6 +38,15 @@ typedef struct {
   unsigned long long peer_meta[B200_MAX_WORLD];   // uint2 [cap_rows]: {src<<24|slot, weight}
   unsigned long long peer_ready[B200_MAX_WORLD];  // uint32 [cap_mtiles] rows landed per M-tile
   int* group_rows_out;            // [e_local] rows per local expert (for the second GEMM)
+  // Iteration state kept on the device (so that a captured CUDA graph can be replayed):
+  // when iter_ptr is set, the kernel reads it = *iter_ptr, uses epoch = it + 1 and adds
+  // (it & 1) * stride to every per-parity pointer above (which then name parity 0).
+  const uint32_t* iter_ptr;
+  unsigned long long stride_counts;   // bytes between the two parity copies of counts_all
+  unsigned long long stride_flag;     // ... of counts_flag
+  unsigned long long stride_recv;     // ... of the receive buffer
+  unsigned long long stride_meta;     // ... of the row metadata
+  unsigned long long stride_ready;    // ... of the tile-ready counters
   unsigned long long* trace;      // optional [2 + 2*trace_tiles]: [0] kernel start (ns), [1] summed producer
                                   // stall (ns), [2 + t] time M-tile t was first seen complete,
                                   // [2 + trace_tiles + t] time this rank last published rows of its own tile t
@@ -52,6 +61,8 @@ typedef struct {
   int max_slots;                  // T*topk of the largest rank (bounds check)
   unsigned long long peer_out[B200_MAX_WORLD];      // bf16 [T*topk, D] slot buffer per rank
   unsigned long long peer_arrived[B200_MAX_WORLD];  // uint32 arrival counter per rank
+  const uint32_t* iter_ptr;       // when set: row_meta names parity 0 and (it & 1) * stride_meta is added
+  unsigned long long stride_meta;
 } b200_combine_args;
 
 typedef struct {

@@ -152,6 +152,12 @@ struct PlanPushArgs {
   unsigned long long peer_flags[B200_MAX_WORLD];   // uint32 [world] flags on each rank
   int* status;
   unsigned long long wait_budget_ns;
+  // Device-side iteration state: when iter_ptr is set, it = *iter_ptr replaces the two
+  // stamps above (epoch = it + 1, need = max(it - 1, 0)) and the peer tables above name
+  // parity 0; (it & 1) * stride selects the copy in use.
+  const uint32_t* iter_ptr;
+  unsigned long long stride_counts;
+  unsigned long long stride_flags;
 };
 
 __global__ void plan_finalize_kernel(const int* __restrict__ topk_idx,
@@ -171,19 +177,27 @@ __global__ void plan_finalize_kernel(const int* __restrict__ topk_idx,
   if (blockIdx.x == 0) {
     for (int e = threadIdx.x; e <= num_experts; e += blockDim.x) bucket_start[e] = s_start[e];
     if (do_push) {
+      uint32_t epoch = push.epoch, need = push.need_iter_done;
+      unsigned long long off_counts = 0, off_flags = 0;
+      if (push.iter_ptr != nullptr) {
+        const uint32_t it = __ldcg(push.iter_ptr);
+        epoch = it + 1u;
+        need = it > 0u ? it - 1u : 0u;
+        if (it & 1u) { off_counts = push.stride_counts; off_flags = push.stride_flags; }
+      }
       WaitCtx w; w.abort_flag = &s_abort; w.status = push.status; w.budget_ns = push.wait_budget_ns;
       if (threadIdx.x < push.world)
-        wait_flag_geq(push.iter_done + threadIdx.x, push.need_iter_done, w, ST_TIMEOUT_ITER);
+        wait_flag_geq(push.iter_done + threadIdx.x, need, w, ST_TIMEOUT_ITER);
       __syncthreads();
       for (int p = 0; p < push.world; ++p) {
-        int* dst = reinterpret_cast<int*>(push.peer_counts[p]) + push.rank * num_experts;
+        int* dst = reinterpret_cast<int*>(push.peer_counts[p] + off_counts) + push.rank * num_experts;
         for (int e = threadIdx.x; e < num_experts; e += blockDim.x) dst[e] = counts[e];
       }
       __syncthreads();
       if (threadIdx.x < push.world) {
         fence_acq_rel_sys();
-        st_release_sys(reinterpret_cast<uint32_t*>(push.peer_flags[threadIdx.x]) + push.rank,
-                       push.epoch);
+        st_release_sys(reinterpret_cast<uint32_t*>(push.peer_flags[threadIdx.x] + off_flags) + push.rank,
+                       epoch);
       }
     }
   }

@@ -54,6 +54,8 @@ class RetireArgs(C.Structure):
         ("ready_counters", C.c_void_p),
         ("num_ready", C.c_int),
         ("ticket", C.c_void_p),
+        ("iter_ptr", C.c_void_p),
+        ("stride_ready", C.c_ulonglong),
     ]
 
 
@@ -183,6 +185,9 @@ class MoELayer(nn.Module):
                        if cfg.gated else None)
         self.group_rows = torch.zeros(EL, **i32)
         self.ticket = torch.zeros(1, **i32)
+        # iteration number, kept on the device: kernels read it and the last kernel of a forward
+        # pass increments it, so launch arguments never change (CUDA-graph replay works)
+        self.iter_dev = torch.zeros(1, **i32)
         n = T * k
         self._plan = Plan(torch.empty(ET, **i32), torch.empty(ET + 1, **i32), torch.empty(n, **i32),
                           torch.empty(n, **i32), torch.empty(n, **i32))
@@ -228,7 +233,8 @@ class MoELayer(nn.Module):
         return self._forward_fused(x)
 
     def route(self, x: torch.Tensor):
-        return router_topk(x, self.router, self.cfg.topk, self.router_bias, self.cfg.renormalize)
+        return router_topk(x, self.router, self.cfg.topk, self.router_bias, self.cfg.renormalize,
+                           status=self.heap.status if (x.is_cuda and self.heap is not None) else None)
 
     def _forward_fused(self, x: torch.Tensor) -> torch.Tensor:
         cfg, heap = self.cfg, self.heap
@@ -238,9 +244,9 @@ class MoELayer(nn.Module):
             raise ValueError(f"x must be [T <= {self.max_tokens}, {D}]")
         if x.dtype != cfg.dtype or not x.is_contiguous():
             x = x.to(cfg.dtype).contiguous()
-        it = self._iteration
-        par = it & 1
         lib = nv.lib()
+        iter_p = self.iter_dev.data_ptr()
+        esz = 2   # bytes per bf16
         st = stream_ptr(x)
         status_p = heap.status.data_ptr()
 
@@ -255,11 +261,12 @@ class MoELayer(nn.Module):
         # 2. plan (+ counts push)
         push = PlanPushArgs()
         push.world, push.rank = W, heap.rank
-        push.epoch = it + 1
-        push.need_iter_done = max(0, it - 1)
         push.iter_done = self.iter_done.data_ptr()
-        push.peer_counts = heap.peer_ptrs(self.counts_all[par])
-        push.peer_flags = heap.peer_ptrs(self.counts_flag[par])
+        push.peer_counts = heap.peer_ptrs(self.counts_all[0])
+        push.peer_flags = heap.peer_ptrs(self.counts_flag[0])
+        push.iter_ptr = iter_p
+        push.stride_counts = W * ET * 4
+        push.stride_flags = W * 4
         push.status = status_p
         push.wait_budget_ns = self._budget_ns
         plan = self._plan
@@ -275,14 +282,19 @@ class MoELayer(nn.Module):
         da.x = x.data_ptr()
         da.send_order = plan.send_order.data_ptr()
         da.topk_weight = wgt.data_ptr()
-        da.counts_all = self.counts_all[par].data_ptr()
-        da.counts_flag = self.counts_flag[par].data_ptr()
-        da.epoch = it + 1
+        da.counts_all = self.counts_all[0].data_ptr()
+        da.counts_flag = self.counts_flag[0].data_ptr()
         da.cap_rows = self.cap_rows
         da.drop_signal = int(self.drop_signal)
-        da.peer_recv = heap.peer_ptrs(self.recv[par])
-        da.peer_meta = heap.peer_ptrs(self.meta[par])
-        da.peer_ready = heap.peer_ptrs(self.ready[par])
+        da.peer_recv = heap.peer_ptrs(self.recv[0])
+        da.peer_meta = heap.peer_ptrs(self.meta[0])
+        da.peer_ready = heap.peer_ptrs(self.ready[0])
+        da.iter_ptr = iter_p
+        da.stride_counts = W * ET * 4
+        da.stride_flag = W * 4
+        da.stride_recv = self.cap_rows * D * esz
+        da.stride_meta = self.cap_rows * 8
+        da.stride_ready = self.cap_mtiles * 4
         da.group_rows_out = self.group_rows.data_ptr()
         if self.trace_arrivals:
             if self._trace is None:
@@ -293,7 +305,9 @@ class MoELayer(nn.Module):
 
         ca = nv.CombineArgs()
         ca.world = W
-        ca.row_meta = self.meta[par].data_ptr()
+        ca.row_meta = self.meta[0].data_ptr()
+        ca.iter_ptr = iter_p
+        ca.stride_meta = self.cap_rows * 8
         ca.out_row_stride = cfg.out_dim
         ca.max_slots = self.max_tokens * k
         ca.peer_out = heap.peer_ptrs(self.out_slots)
@@ -303,7 +317,7 @@ class MoELayer(nn.Module):
         ga.num_groups, ga.K, ga.group_m = EL, D, 0
         ga.status, ga.wait_budget_ns = status_p, self._budget_ns
         ga.cta_pair = self._cta_pair
-        recv = self.recv[par]
+        recv = self.recv[0]
         if cfg.gated:
             F = cfg.ffn_dim
             ga.N, ga.n_out = 2 * F, F
@@ -334,9 +348,10 @@ class MoELayer(nn.Module):
         y = torch.empty((T, cfg.out_dim), dtype=cfg.dtype, device=x.device)
         ra = RetireArgs()
         ra.world, ra.rank = W, heap.rank
-        ra.iter_done_value = it + 1
         ra.peer_iter_done = heap.peer_ptrs(self.iter_done)
-        ra.ready_counters = self.ready[par].data_ptr()
+        ra.ready_counters = self.ready[0].data_ptr()
+        ra.iter_ptr = iter_p
+        ra.stride_ready = self.cap_mtiles * 4
         ra.num_ready = self.cap_mtiles
         ra.ticket = self.ticket.data_ptr()
         n_tiles = (cfg.out_dim + BN - 1) // BN
@@ -344,9 +359,43 @@ class MoELayer(nn.Module):
                                    cfg.out_dim, ptr(y), C.byref(ra), C.c_void_p(status_p),
                                    self._budget_ns, st), "slot reduce launch")
         ev("slot_reduce")
-        self._iteration = it + 1
+        self._iteration += 1
         self.last_routing = (idx, wgt)
         return y
+
+    # ------------------------------------------------------------ CUDA graphs
+    def capture(self, num_tokens: Optional[int] = None) -> None:
+        """Capture one forward pass for ``num_tokens`` tokens into a CUDA graph.
+
+        Every launch argument is fixed (the iteration number and the parity of the
+        double-buffered peer state live in device memory), so the graph can be replayed for
+        every later step with :meth:`replay`.  In a multi-rank job all ranks must capture and
+        replay in step.  The layer is warmed up first: kernel attributes and driver entry
+        points are resolved outside the capture."""
+        T = self.max_tokens if num_tokens is None else int(num_tokens)
+        dev = self.heap.device
+        self._graph_x = torch.zeros((T, self.cfg.hidden_dim), dtype=self.cfg.dtype, device=dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            self._forward_fused(self._graph_x)          # warm-up outside the capture
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._graph_y = self._forward_fused(self._graph_x)
+
+    def replay(self, x: torch.Tensor) -> torch.Tensor:
+        """Run the captured forward pass on ``x`` (copied into the graph's static input);
+        returns the graph's static output tensor, valid until the next replay."""
+        if getattr(self, "_graph", None) is None:
+            raise RuntimeError("call capture() first")
+        if x.shape != self._graph_x.shape:
+            raise ValueError(f"the graph was captured for input shape {tuple(self._graph_x.shape)}")
+        self._graph_x.copy_(x, non_blocking=True)
+        self._graph.replay()
+        self._iteration += 1
+        return self._graph_y
 
     def arrival_report(self) -> dict:
         """Overlap evidence from the last forward run with ``trace_arrivals = True``: when (relative

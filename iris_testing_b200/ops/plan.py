@@ -26,6 +26,9 @@ class PlanPushArgs(C.Structure):
         ("peer_flags", C.c_ulonglong * nv.MAX_WORLD),
         ("status", C.c_void_p),
         ("wait_budget_ns", C.c_ulonglong),
+        ("iter_ptr", C.c_void_p),
+        ("stride_counts", C.c_ulonglong),
+        ("stride_flags", C.c_ulonglong),
     ]
 
 

@@ -89,3 +89,25 @@ def test_dropped_arrival_signal_times_out_with_status():
         layer.check_status()
     # the context is still usable
     assert float(torch.ones(4, device=heap.device).sum()) == 4.0
+
+
+@pytest.mark.parametrize("gated", [True, False])
+def test_cuda_graph_replay_matches_eager(gated):
+    """The forward pass captured once replays correctly for every later step: the iteration
+    number and the buffer parity are read from device memory, not baked into the launches."""
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.utils import gen_local_tokens
+    cfg = MoEConfig(hidden_dim=256, ffn_dim=512 if gated else 0, num_experts=8, topk=2, gated=gated)
+    layer, heap = _make(cfg, 300)
+    dev = heap.device
+    xs = [gen_local_tokens(1, 300, 256, torch.bfloat16, dev, i, 0, "normal") for i in range(5)]
+    refs = [_dense(layer, x) for x in xs]
+    y0 = layer(xs[0])                                     # eager step before the capture
+    assert torch.allclose(y0.float(), refs[0], atol=3e-2 * float(refs[0].abs().max()), rtol=3e-2)
+    layer.capture(300)
+    for i in (1, 2, 3):                                   # odd and even iterations
+        y = layer.replay(xs[i]).clone()
+        assert torch.allclose(y.float(), refs[i], atol=3e-2 * float(refs[i].abs().max()), rtol=3e-2), i
+    y4 = layer(xs[4])                                     # eager again after replays
+    assert torch.allclose(y4.float(), refs[4], atol=3e-2 * float(refs[4].abs().max()), rtol=3e-2)
+    layer.check_status()

@@ -92,6 +92,12 @@ def test_fused_layer(heap, D: int, F: int, e_local: int, topk: int, T: int) -> N
             ref = cpu_ref.dense_moe_ref(x, layer.router, topk, w_single=torch.cat(_gather(w1)))
         err, scale = float((y.float() - ref).abs().max()), float(ref.abs().max())
         assert err <= 3e-2 * scale, (rank, i, err, scale)
+    # the same step replayed from a CUDA graph captured once (all ranks capture and replay in step)
+    layer.capture(T)
+    for _ in range(3):
+        y = layer.replay(x)
+        err = float((y.float() - ref).abs().max())
+        assert err <= 3e-2 * scale, (rank, "graph", err, scale)
     layer.check_status()
 
 
