@@ -3,7 +3,7 @@
     python -m iris_testing_b200.bench_kernels gemm   [--groups 4 --rows 4096 --n 2048 --k 4096 --gated 0]
     python -m iris_testing_b200.bench_kernels router [--tokens 16384 --hidden 4096 --experts 8 --topk 2]
     python -m iris_testing_b200.bench_kernels plan   [--tokens 16384 --experts 8 --topk 2]
-    python -m iris_testing_b200.bench_kernels layer  [--model mixtral-8x7b --tokens 16384]
+    python -m iris_testing_b200.bench_kernels layer  [--model mixtral-8x7b --tokens 16384 --graph 0]
 
 Each sub-command warms up, times ``--iters`` launches with CUDA events and prints one JSON
 line: achieved TFLOP/s or GB/s and the fraction of the measured peaks (``MEASURED_PEAKS.json``
@@ -100,12 +100,17 @@ def cmd_layer(a) -> dict:
     heap = SymmetricHeap(heap_bytes_needed(cfg, a.tokens) + (64 << 20))
     layer = MoELayer(cfg, max_tokens=a.tokens, heap=heap, router_std=None)
     x = gen_local_tokens(1, a.tokens, cfg.hidden_dim, torch.bfloat16, heap.device, 0, 0, "normal")
-    ms = time_launches(lambda: layer(x), a.iters)
+    if a.graph:                                   # replay a captured CUDA graph instead of 6 launches
+        layer.capture(a.tokens)
+        ms = time_launches(lambda: layer.replay(x), a.iters)
+    else:
+        ms = time_launches(lambda: layer(x), a.iters)
     layer.check_status()
     flops = 2.0 * a.tokens * cfg.topk * cfg.hidden_dim * 3 * cfg.ffn_dim
     pk = peaks()
     tf = flops / ms / 1e9
-    return dict(kernel="MoELayer.forward (1 GPU)", model=a.model, tokens=a.tokens, ms=round(ms, 4),
+    return dict(kernel="MoELayer.forward (1 GPU)" + (", CUDA graph replay" if a.graph else ""),
+                model=a.model, tokens=a.tokens, ms=round(ms, 4),
                 tflops=round(tf, 1), frac_of_peak=round(tf / pk["tflops"], 3),
                 frac_of_sustained=round(tf / pk["tflops_sustained"], 3) if pk["tflops_sustained"] else None,
                 peak=pk["kind"])
@@ -126,6 +131,7 @@ def main() -> None:
     p.add_argument("--topk", type=int, default=2)
     l = sub.add_parser("layer")
     l.add_argument("--model", default="mixtral-8x7b"); l.add_argument("--tokens", type=int, default=16384)
+    l.add_argument("--graph", type=int, default=0)
     for s in (g, r, p, l):
         s.add_argument("--iters", type=int, default=5)
     a = ap.parse_args()
