@@ -46,7 +46,8 @@ constexpr int STG_ROW_BYTES = STG_COLS * 2 + 16;      // padded: conflict-free 1
 constexpr int STG_BYTES = BM * STG_ROW_BYTES;         // 18 KiB
 constexpr int TMEM_COLS = 512;                        // two 256-column accumulators
 constexpr int NUM_THREADS_PLAIN = 192;
-constexpr int NUM_THREADS_FUSED = 320;
+constexpr int SENDER_WARPS = 4;    // token-sender warps per CTA in the fused-dispatch build
+constexpr int NUM_THREADS_FUSED = NUM_THREADS_PLAIN + SENDER_WARPS * 32;
 constexpr int SEND_ROWS = 32;   // rows per sender work unit (aligned in the destination expert's row space)
 
 struct __align__(16) ControlSmem {
@@ -631,13 +632,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   } else {
     // ------------------------------------------------------------ token senders
     if constexpr (FUSED) {
-      const int stid = tid - 6 * 32;            // 0..127 inside the sender group
+      const int stid = tid - NUM_THREADS_PLAIN;   // index inside the sender group
       const int swarp = stid >> 5;
       const int ET = da.world * da.e_local;
       const int total_units = c.total_units;
       const int k16 = ga.K / 8;                 // 16-byte chunks per token row
       int bcur = 0;
-      // The loop bound is uniform over the four sender warps (they meet at a
+      // The loop bound is uniform over the sender warps (they meet at a
       // named barrier per unit), so it must not depend on the abort flag.
       for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
         while (bcur < ET && u >= c.b_unit_start[bcur + 1]) ++bcur;
@@ -654,7 +655,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
         const int drow0 = c.b_dst_row[bcur];
         uint8_t* recv = reinterpret_cast<uint8_t*>(da.peer_recv[dst]);
         uint2* meta = reinterpret_cast<uint2*>(da.peer_meta[dst]);
-        for (int p = p_lo + swarp; p < p_hi; p += 4) {
+        for (int p = p_lo + swarp; p < p_hi; p += SENDER_WARPS) {
           const int flat = __ldg(da.send_order + send0 + p);
           const int t = flat / da.topk;
           const int drow = drow0 + p;
@@ -680,8 +681,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
             meta[drow] = mv;
           }
         }
-        // all four sender warps have stored their rows of this unit
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // all sender warps have stored their rows of this unit
+        asm volatile("bar.sync 1, %0;" ::"n"(SENDER_WARPS * 32) : "memory");
         if (stid == 0 && !da.drop_signal) {
           fence_acq_rel_sys();
           red_add_release_sys(reinterpret_cast<uint32_t*>(da.peer_ready[dst]) +
