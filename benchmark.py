@@ -33,9 +33,9 @@ import torch.distributed as dist
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 
 from iris_testing_b200.utils import (alloc_return_buffers, alloc_shmem_buffers, allreduce_max,  # noqa: E402
-                                     allreduce_sum, build_dst_offsets, gen_local_tokens, gen_router,
-                                     mark, masked_stats, reset_dispatch_flags, route_and_pack,
-                                     sync_and_check, zipf_expert_bias)
+                                     allreduce_sum, gen_local_tokens, gen_router, mark, masked_stats,
+                                     reset_dispatch_flags, route_and_pack, sync_and_check,
+                                     zipf_expert_bias)
 
 
 def env_int(name: str, default: int) -> int:
@@ -132,9 +132,12 @@ def run_a2a(rank: int, world: int, dev: torch.device) -> None:
             return per.view(x.shape[0], topk, -1).sum(1).to(dt)
         return meta["recv_payload"]
 
+    trace = env_int("TRACE", 0)
     ok = True
     err = None
     try:
+        if trace:
+            mark("warm-up: custom path")
         for _ in range(warmup):
             custom_once()
         torch.cuda.synchronize()

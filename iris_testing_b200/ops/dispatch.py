@@ -14,7 +14,6 @@ from __future__ import annotations
 
 import ctypes as C
 import os
-from typing import Optional
 
 import torch
 import torch.distributed as dist

@@ -7,7 +7,6 @@ any object with ``zeros(shape, dtype)`` and ``get_heap_bases()`` (the CPU tests 
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
 
 import torch
 

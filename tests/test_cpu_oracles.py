@@ -1,6 +1,4 @@
 """CPU tests of the PyTorch restatements and host helpers (no GPU, no process group)."""
-import os
-
 import pytest
 import torch
 

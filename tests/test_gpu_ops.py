@@ -166,7 +166,7 @@ def test_unfused_pipeline_ragged_single_gpu(dev, heap):
     from iris_testing_b200.ops import cpu_ref, custom_a2a, expert, shuffle, unshuffle
     from iris_testing_b200.ops.combine import padded_return, weighted_gather
     from iris_testing_b200.utils import (alloc_return_buffers, alloc_shmem_buffers, gen_local_tokens,
-                                         gen_local_weights, gen_router, masked_stats, route_and_pack)
+                                         gen_local_weights, gen_router, route_and_pack)
     D, E, k, T = 256, 8, 2, 300
     x = gen_local_tokens(1, T, D, torch.bfloat16, dev, 1, 0, "normal")
     router = gen_router(D, E, torch.bfloat16, dev, 1, std=None)
