@@ -101,6 +101,9 @@ __device__ __forceinline__ bool decode_tile(const ControlSmem& c, int G, int TN,
   g = cursor;
   const int tm = c.g_sched_start[g + 1] - c.g_sched_start[g];
   const int j = idx - TN * c.g_sched_start[g];
+  // even out the chunks of this group: 16 M-tiles with a target of 12 become 8 + 8, not 12 + 4
+  const int nchunks = (tm + gm - 1) / gm;
+  gm = (tm + nchunks - 1) / nchunks;
   const int chunk_tiles = gm * TN;
   const int ch = j / chunk_tiles;
   const int r = j - ch * chunk_tiles;
