@@ -236,7 +236,7 @@ __global__ void shuffle_kernel(uint4* token_buf, uint4* packed, const int* pca,
 // ---------------------------------------------------------------------------
 // Slot reduction ending the fused combine: wait (bounded) until `expected`
 // (row, n-tile) units have landed in out_slots, then y[t] = sum_slot
-// out_slots[t*k+slot] in slot order (deterministic).  The last block to finish
+// out_slots[dst_slot[t*k+slot]] in slot order (deterministic).  The last block to finish
 // re-arms the per-iteration state (arrival counter, this parity's tile-ready
 // counters) and tells every peer that this rank has retired the iteration.
 // ---------------------------------------------------------------------------
@@ -253,8 +253,8 @@ struct RetireArgs {
   unsigned long long stride_ready;   // bytes between the two parity copies of ready_counters
 };
 
-__global__ void slot_reduce_kernel(const __nv_bfloat16* out_slots, uint32_t* arrived,
-                                   uint32_t expected, int T, int topk, int H,
+__global__ void slot_reduce_kernel(const __nv_bfloat16* out_slots, const int* __restrict__ dst_slot,
+                                   uint32_t* arrived, uint32_t expected, int T, int topk, int H,
                                    __nv_bfloat16* __restrict__ y, RetireArgs ra, int* status,
                                    unsigned long long budget_ns) {
   __shared__ int s_abort;
@@ -273,8 +273,11 @@ __global__ void slot_reduce_kernel(const __nv_bfloat16* out_slots, uint32_t* arr
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
         for (int s = 0; s < topk; ++s) {
-          const uint4 v = ld_16(reinterpret_cast<const uint4*>(
-              out_slots + (static_cast<size_t>(t) * topk + s) * H + c0));
+          // results sit at the row's position in the packed send order (dst_slot), or at
+          // t*topk+s when no map is given
+          const size_t row = dst_slot != nullptr ? static_cast<size_t>(__ldg(dst_slot + t * topk + s))
+                                                 : static_cast<size_t>(t) * topk + s;
+          const uint4 v = ld_16(reinterpret_cast<const uint4*>(out_slots + row * H + c0));
           const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -417,7 +420,8 @@ int b200_shuffle(void* token_buf, void* packed, const int* pca, const void* coun
   return static_cast<int>(cudaGetLastError());
 }
 
-int b200_slot_reduce(const void* out_slots, void* arrived, unsigned int expected, int T, int topk,
+int b200_slot_reduce(const void* out_slots, const int* dst_slot, void* arrived, unsigned int expected,
+                     int T, int topk,
                      int hidden_dim, void* y, const b200::RetireArgs* ra, int* status,
                      unsigned long long budget_ns, void* stream) {
   if (hidden_dim % 8 != 0 || ra == nullptr) return -1;
@@ -425,7 +429,7 @@ int b200_slot_reduce(const void* out_slots, void* arrived, unsigned int expected
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 4) blocks = 148 * 4;
   b200::slot_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(out_slots), static_cast<uint32_t*>(arrived), expected, T,
+      static_cast<const __nv_bfloat16*>(out_slots), dst_slot, static_cast<uint32_t*>(arrived), expected, T,
       topk, hidden_dim, static_cast<__nv_bfloat16*>(y), *ra, status, budget_ns);
   return static_cast<int>(cudaGetLastError());
 }

@@ -679,7 +679,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
           }
           if (lane == 0) {
             uint2 mv;
-            mv.x = (static_cast<uint32_t>(da.rank) << 24) | static_cast<uint32_t>(flat);
+            // the row's position in this rank's packed send order: results come back to that
+            // position, so the rows of one (destination, expert) bucket return to consecutive
+            // addresses (sequential remote writes) instead of to scattered token slots
+            mv.x = (static_cast<uint32_t>(da.rank) << 24) | static_cast<uint32_t>(send0 + p);
             mv.y = __float_as_uint(__ldg(da.topk_weight + flat));
             meta[drow] = mv;
           }

@@ -35,7 +35,7 @@ typedef struct {
   int cap_rows;                   // receive capacity (rows) of every rank
   int drop_signal;                // testing aid: do not signal tile arrival
   unsigned long long peer_recv[B200_MAX_WORLD];   // bf16 [cap_rows, K]
-  unsigned long long peer_meta[B200_MAX_WORLD];   // uint2 [cap_rows]: {src<<24|slot, weight}
+  unsigned long long peer_meta[B200_MAX_WORLD];   // uint2 [cap_rows]: {src<<24|send position, weight}
   unsigned long long peer_ready[B200_MAX_WORLD];  // uint32 [cap_mtiles] rows landed per M-tile
   int* group_rows_out;            // [e_local] rows per local expert (for the second GEMM)
   // Iteration state kept on the device (so that a captured CUDA graph can be replayed):
@@ -56,10 +56,10 @@ typedef struct {
 // Combine side (epilogue of the second grouped GEMM).
 typedef struct {
   int world;
-  const void* row_meta;           // uint2 [rows]: {src<<24|slot, weight}
+  const void* row_meta;           // uint2 [rows]: {src<<24|row in the source's return buffer, weight}
   long long out_row_stride;       // elements between slot rows (= model dim)
   int max_slots;                  // T*topk of the largest rank (bounds check)
-  unsigned long long peer_out[B200_MAX_WORLD];      // bf16 [T*topk, D] slot buffer per rank
+  unsigned long long peer_out[B200_MAX_WORLD];      // bf16 [T*topk, D] return buffer per rank (send order)
   unsigned long long peer_arrived[B200_MAX_WORLD];  // uint32 arrival counter per rank
   const uint32_t* iter_ptr;       // when set: row_meta names parity 0 and (it & 1) * stride_meta is added
   unsigned long long stride_meta;

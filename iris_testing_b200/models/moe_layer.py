@@ -12,7 +12,7 @@ Forward pass on B200 (five launches, no host synchronisation):
 4. GEMM2+combine   ONE kernel: second grouped GEMM whose epilogue scales each row by
                    its top-k weight and stores it straight into the source rank's slot
                    buffer, counting arrivals there
-5. slot reduce     waits for the arrivals, sums the k slots per token, retires the
+5. slot reduce     waits for the arrivals, gathers and sums the k results per token, retires the
                    iteration (re-arms counters, tells peers the parity slot is free)
 
 The reference project wires none of this together (its intended forward pass is
@@ -193,7 +193,7 @@ class MoELayer(nn.Module):
                           torch.empty(n, **i32), torch.empty(n, **i32))
         self._slot_reduce = declare(
             "b200_slot_reduce",
-            [C.c_void_p, C.c_void_p, C.c_uint, C.c_int, C.c_int, C.c_int, C.c_void_p,
+            [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_int, C.c_int, C.c_int, C.c_void_p,
              C.POINTER(RetireArgs), C.c_void_p, C.c_ulonglong, C.c_void_p])
         self._ctas = sm_count(dev)
         pair = cfg.cta_pair
@@ -355,7 +355,8 @@ class MoELayer(nn.Module):
         ra.num_ready = self.cap_mtiles
         ra.ticket = self.ticket.data_ptr()
         n_tiles = (cfg.out_dim + BN - 1) // BN
-        nv.check(self._slot_reduce(ptr(self.out_slots), ptr(self.arrived), T * k * n_tiles, T, k,
+        nv.check(self._slot_reduce(ptr(self.out_slots), ptr(plan.dst_slot), ptr(self.arrived),
+                                   T * k * n_tiles, T, k,
                                    cfg.out_dim, ptr(y), C.byref(ra), C.c_void_p(status_p),
                                    self._budget_ns, st), "slot reduce launch")
         ev("slot_reduce")
