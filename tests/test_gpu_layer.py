@@ -111,3 +111,25 @@ def test_cuda_graph_replay_matches_eager(gated):
     y4 = layer(xs[4])                                     # eager again after replays
     assert torch.allclose(y4.float(), refs[4], atol=3e-2 * float(refs[4].abs().max()), rtol=3e-2)
     layer.check_status()
+
+
+def test_phase_timing_and_arrival_trace():
+    """The profiling hooks: per-phase CUDA-event times and the per-tile arrival trace."""
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.utils import gen_local_tokens
+    cfg = MoEConfig(hidden_dim=256, ffn_dim=512, num_experts=4, topk=2)
+    layer, heap = _make(cfg, 1024)
+    x = gen_local_tokens(1, 1024, 256, torch.bfloat16, heap.device, 0, 0, "normal")
+    layer(x)
+    layer.profile = True
+    layer.trace_arrivals = True
+    y = layer(x)
+    phases = layer.phase_times_us()
+    assert list(phases) == ["router", "plan", "dispatch+gemm1", "gemm2+combine", "slot_reduce"]
+    assert all(v > 0 for v in phases.values())
+    rep = layer.arrival_report()
+    assert rep["tiles"] == sum((int(r) + 127) // 128 for r in layer.group_rows.tolist())
+    assert 0 <= rep["first_us"] <= rep["last_us"] and rep["own_last_published_us"] >= rep["own_first_published_us"]
+    ref = _dense(layer, x)
+    assert torch.allclose(y.float(), ref, atol=3e-2 * float(ref.abs().max()), rtol=3e-2)
+    layer.check_status()
