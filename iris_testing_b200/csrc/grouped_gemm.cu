@@ -324,6 +324,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   if constexpr (FUSED) {
     if (tid == 0 && c.g_row_start[G] > da.cap_rows) {
       report_status(w.status, ST_OVERFLOW);
+      if (w.status != nullptr) atomicMax(w.status + 1, c.g_row_start[G]);   // rows that were needed
       c.abort_flag = 1;
     }
     __syncthreads();

@@ -175,11 +175,13 @@ class SymmetricHeap:
 
     def check_status(self, reset: bool = True) -> None:
         """Raise if any kernel recorded an error (timeout, overflow, bad index) on this rank."""
-        code = int(self.status[0].item())
+        st = self.status.tolist()
+        code = int(st[0])
         if code != 0:
             if reset:
                 self.status.zero_()
-            raise nv.NativeError(f"rank {self.rank}: device status {code}: {nv.status_message(code)}")
+            extra = f" (rows needed on this rank: {st[1]})" if code == 10 and st[1] > 0 else ""
+            raise nv.NativeError(f"rank {self.rank}: device status {code}: {nv.status_message(code)}{extra}")
 
     def close(self) -> None:
         if self._closed:

@@ -173,7 +173,9 @@ def test_unfused_pipeline_ragged_single_gpu(dev, heap):
     w = gen_local_weights(E, D, D, torch.bfloat16, dev, 1, 0, std=0.05)
     payload, counts, dst_off, _, idx, wgt, plan = route_and_pack(x, router, k, 1, E)
     cap = int(counts.max().item())
-    b = alloc_shmem_buffers(heap, 1, E, cap, D, torch.bfloat16)
+    guard_lo = heap.zeros((4096,), torch.int32); guard_lo.fill_(0x5A5A5A5A)     # canaries around the
+    b = alloc_shmem_buffers(heap, 1, E, cap, D, torch.bfloat16)                   # symmetric buffers
+    guard_hi = heap.zeros((4096,), torch.int32); guard_hi.fill_(0x5A5A5A5A)
     custom_a2a(payload, counts, dst_off, b.pca, b.token_buf, b.counts_ready, b.token_sync,
                b.heap_bases, E, cap)
     packed, rows = shuffle(b.token_buf, b.pca, b.token_sync, b.counts_ready)
@@ -189,6 +191,7 @@ def test_unfused_pipeline_ragged_single_gpu(dev, heap):
     ref = cpu_ref.dense_moe_ref(x, router, k, w_single=w)
     assert torch.allclose(y.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
     heap.check_status()
+    assert bool((guard_lo == 0x5A5A5A5A).all()) and bool((guard_hi == 0x5A5A5A5A).all())
     # capacity too small: rows beyond CAP are dropped and the status word says so
     small = alloc_shmem_buffers(heap, 1, E, max(cap // 2, 1), D, torch.bfloat16)
     custom_a2a(payload, counts, dst_off, small.pca, small.token_buf, small.counts_ready,
