@@ -456,3 +456,5 @@ int b200_barrier(const unsigned long long* peer_flags, void* local_flags, int ra
 }
 
 }  // extern "C"
+
+extern "C" int b200_abi_size_retire_args() { return static_cast<int>(sizeof(b200::RetireArgs)); }

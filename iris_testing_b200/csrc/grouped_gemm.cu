@@ -864,3 +864,11 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
 int b200_gemm_smem_bytes() { return b200::Geo<1>::SMEM_BYTES; }
 
 }  // extern "C"
+
+// Sizes of the argument blocks, so that a binding in another language can check its mirrors.
+extern "C" void b200_abi_sizes_gemm(int* out) {
+  out[0] = static_cast<int>(sizeof(b200_gemm_args));
+  out[1] = static_cast<int>(sizeof(b200_dispatch_args));
+  out[2] = static_cast<int>(sizeof(b200_combine_args));
+  out[3] = static_cast<int>(sizeof(b200_router_args));
+}

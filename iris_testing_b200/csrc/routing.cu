@@ -275,6 +275,8 @@ int b200_pack_rows(const void* x, const int* send_order, int n_flat, int topk, i
 
 }  // extern "C"
 
+extern "C" int b200_abi_size_plan_push_args() { return static_cast<int>(sizeof(b200::PlanPushArgs)); }
+
 // ---------------------------------------------------------------------------
 // Allocation-free plan (declared and documented in plan_noalloc.h).
 // ---------------------------------------------------------------------------

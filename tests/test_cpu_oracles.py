@@ -177,3 +177,17 @@ def test_interleave_gate_up_layout():
     assert torch.equal(w13[:, :128], w1.transpose(1, 2)[:, :128])
     assert torch.equal(w13[:, 128:256], w3.transpose(1, 2)[:, :128])
     assert torch.equal(w13[:, 256:384], w1.transpose(1, 2)[:, 128:])
+
+
+def test_capacity_and_heap_sizing():
+    from iris_testing_b200.models import default_cap_rows, heap_bytes_needed
+    cfg = preset("mixtral-8x7b", world_size=8)
+    worst = default_cap_rows(cfg, 16384)
+    assert worst == 8 * 16384 * 2 and worst % 128 == 0          # every token of every rank
+    import dataclasses
+    tight = dataclasses.replace(cfg, capacity_factor=1.25)
+    assert default_cap_rows(tight, 16384) < worst
+    assert default_cap_rows(tight, 16384) >= int(1.25 * 16384 * 2)
+    need = heap_bytes_needed(cfg, 16384)
+    assert need > 2 * worst * 4096 * 2                           # two parity copies of the receive buffer
+    assert heap_bytes_needed(cfg, 16384, cap_rows=1024) < need
