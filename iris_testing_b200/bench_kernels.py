@@ -4,6 +4,7 @@
     python -m iris_testing_b200.bench_kernels router [--tokens 16384 --hidden 4096 --experts 8 --topk 2]
     python -m iris_testing_b200.bench_kernels plan   [--tokens 16384 --experts 8 --topk 2]
     python -m iris_testing_b200.bench_kernels layer  [--model mixtral-8x7b --tokens 16384 --graph 0]
+    python -m iris_testing_b200.bench_kernels pipeline [--tokens 8192 --hidden 2048 --experts 8 --topk 2]
 
 Each sub-command warms up, times ``--iters`` launches with CUDA events and prints one JSON
 line: achieved TFLOP/s or GB/s and the fraction of the measured peaks (``MEASURED_PEAKS.json``
@@ -116,6 +117,47 @@ def cmd_layer(a) -> dict:
                 peak=pk["kind"])
 
 
+def cmd_pipeline(a) -> dict:
+    """The unfused, reference-shaped pipeline on one GPU, one launch of every stand-alone kernel:
+    router (CUDA-core variant) -> plan -> pack -> padded dispatch -> shuffle -> expert GEMM ->
+    SiLU gate -> unshuffle -> padded return -> weighted gather, plus the barrier."""
+    from .ops import custom_a2a, expert, router_topk, shuffle, silu_gate, unshuffle
+    from .ops.combine import padded_return, weighted_gather
+    from .parallel.symm import SymmetricHeap
+    from .utils import (alloc_return_buffers, alloc_shmem_buffers, gen_local_tokens, gen_local_weights,
+                        gen_router, reset_dispatch_flags, route_and_pack)
+    dev = torch.device("cuda")
+    T, D, E, k = a.tokens, a.hidden, a.experts, a.topk
+    x = gen_local_tokens(1, T, D, torch.bfloat16, dev, 0, 0, "normal")
+    router = gen_router(D, E, torch.bfloat16, dev, 0, std=None)
+    w = gen_local_weights(E, D, D, torch.bfloat16, dev, 0, 0)
+    cap = 2 * T * k // E
+    heap = SymmetricHeap(2 * E * cap * D * 2 + (256 << 20))
+    b = alloc_shmem_buffers(heap, 1, E, cap, D, torch.bfloat16)
+    r = alloc_return_buffers(heap, 1, E, cap, D, torch.bfloat16)
+
+    def once():
+        router_topk(x, router, k, force_simple=True)
+        payload, counts, dst_off, _, idx, wgt, plan = route_and_pack(x, router, k, 1, E)
+        reset_dispatch_flags(b)
+        r.ret_sync.zero_()
+        heap.barrier(host_sync=False)
+        custom_a2a(payload, counts, dst_off, b.pca, b.token_buf, b.counts_ready, b.token_sync,
+                   b.heap_bases, E, cap)
+        packed, rows = shuffle(b.token_buf, b.pca, b.token_sync, b.counts_ready, max_rows=T * k,
+                               status=heap.status)
+        out = expert(packed, w, rows)
+        out = silu_gate(out, out)
+        out_buf = unshuffle(out, b.pca, cap)
+        padded_return(out_buf, b.pca, r.ret_buf, r.ret_sync, b.heap_bases)
+        return weighted_gather(r.ret_buf, plan, idx, wgt, r.ret_sync, 1, cap, status=heap.status)
+
+    ms = time_launches(once, a.iters, warmup=2)
+    heap.check_status()
+    return dict(kernel="unfused pipeline (1 GPU)", tokens=T, hidden=D, experts=E, topk=k, cap=cap,
+                ms=round(ms, 4), payload_mb=round(T * k * D * 2 / 1e6, 1))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -132,11 +174,14 @@ def main() -> None:
     l = sub.add_parser("layer")
     l.add_argument("--model", default="mixtral-8x7b"); l.add_argument("--tokens", type=int, default=16384)
     l.add_argument("--graph", type=int, default=0)
-    for s in (g, r, p, l):
+    q = sub.add_parser("pipeline")
+    q.add_argument("--tokens", type=int, default=8192); q.add_argument("--hidden", type=int, default=2048)
+    q.add_argument("--experts", type=int, default=8); q.add_argument("--topk", type=int, default=2)
+    for s in (g, r, p, l, q):
         s.add_argument("--iters", type=int, default=5)
     a = ap.parse_args()
     torch.cuda.set_device(0)
-    out = dict(gemm=cmd_gemm, router=cmd_router, plan=cmd_plan, layer=cmd_layer)[a.cmd](a)
+    out = dict(gemm=cmd_gemm, router=cmd_router, plan=cmd_plan, layer=cmd_layer, pipeline=cmd_pipeline)[a.cmd](a)
     print(json.dumps(out), flush=True)
 
 
