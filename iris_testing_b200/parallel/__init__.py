@@ -4,6 +4,7 @@ from .baseline_nccl import (AllToAllMoEBaseline, ExchangeBuffers, exchange_count
                             exchange_payload, init_baseline_buffers, relayout_to_token_buf,
                             run_baseline)
 from .gloo_moe import moe_forward_gloo, padded_exchange, pair_message_rows
+from .health import HealthMonitor
 
 
 def SymmetricHeap(*args, **kwargs):

@@ -41,3 +41,28 @@ def test_benchmark_driver_correctness_report():
                                        WARMUP="2", ITERS="3", CHECK="1", TOKEN_DIST="normal"))
     assert res.returncode == 0 and "PASS" in res.stdout and "FAIL" not in res.stdout, \
         res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_rank_leaving_between_steps_is_detected_on_the_host():
+    """Failure detection without a GPU fault: a rank exits between steps; the survivor learns of
+    it from the host-side monitor (short gloo timeout) before launching its next step."""
+    if 2 not in _worlds():
+        pytest.skip("needs 2 GPUs")
+    env = dict(os.environ, WORLD_SIZE="2", NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", MASTER_PORT="29655")
+    procs = []
+    for r in range(2):
+        e = dict(env, RANK=str(r), LOCAL_RANK=str(r))
+        procs.append(subprocess.Popen([sys.executable, str(ROOT / "tests" / "_rank_leaves_worker.py")], env=e,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=str(ROOT)))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=180)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+            out += "\n[killed after timeout]"
+        outs.append(out)
+    assert "rank1: leaving between steps" in outs[1], outs[1][-1500:]
+    assert "peer loss detected on the host before step 2" in outs[0], outs[0][-1500:]
+    assert "rank0: steps_done=2" in outs[0] and "rank0: OK" in outs[0], outs[0][-1500:]
