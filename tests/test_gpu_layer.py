@@ -27,7 +27,8 @@ def _dense(layer, x):
 @pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("D,F,E,k,gated,T", [
     (256, 512, 8, 2, True, 200), (256, 0, 4, 1, False, 77), (2048, 1408, 32, 4, True, 2048),
-    (512, 256, 64, 8, True, 1000), (128, 0, 8, 2, False, 128), (1024, 1024, 2, 2, True, 3000)])
+    (512, 256, 64, 8, True, 1000), (128, 0, 8, 2, False, 128), (1024, 1024, 2, 2, True, 3000),
+    (128, 128, 128, 2, True, 700), (72, 128, 8, 3, True, 333), (200, 0, 16, 4, False, 129)])
 def test_fused_layer_matches_dense_reference(D, F, E, k, gated, T, pair):
     from iris_testing_b200.config import MoEConfig
     from iris_testing_b200.utils import gen_local_tokens
