@@ -15,8 +15,14 @@
 //               buffer over NVLink, then signal the M-tile they landed in.
 //
 // Epilogues: plain store, SiLU-gated (gate/up column blocks interleaved per
-// 256-wide weight tile) and "combine": scale by the row's top-k weight and
-// store straight into the source rank's slot buffer, then count arrivals there.
+// 256-wide weight tile), "combine" (scale by the row's top-k weight and store
+// straight into the source rank's return buffer at the row's send-order
+// position, then count arrivals there) and "router" (one thread per token:
+// softmax over the accumulator row, top-k in registers).
+//
+// Two geometries (template parameter CG): one CTA per 128 x 256 tile, or a
+// pair of CTAs (cluster of 2, tcgen05 cta_group::2) per 256 x 256 tile in which
+// each CTA stages its own half of both operands with plain TMA loads.
 //
 // Role of this file relative to the reference project: the persistent grouped
 // GEMM sketched in kernels.py:207-289 / layers/expert.py:6-65, the token

@@ -1,6 +1,6 @@
 """``MoELayer``: one expert-parallel Mixture-of-Experts block.
 
-Forward pass on B200 (five launches, no host synchronisation):
+Forward pass on B200 (six launches, no host synchronisation):
 
 1. router          softmax -> top-k (indices + weights)
 2. plan            per-expert counts, stable bucket ranks, send order; pushes this
@@ -10,8 +10,8 @@ Forward pass on B200 (five launches, no host synchronisation):
                    tcgen05 grouped GEMM of the same kernel consumes tiles as they land
                    (SiLU-gate epilogue -> hidden activation, local HBM)
 4. GEMM2+combine   ONE kernel: second grouped GEMM whose epilogue scales each row by
-                   its top-k weight and stores it straight into the source rank's slot
-                   buffer, counting arrivals there
+                   its top-k weight and stores it straight into the source rank's return
+                   buffer (at the row's send-order position), counting arrivals there
 5. slot reduce     waits for the arrivals, gathers and sums the k results per token, retires the
                    iteration (re-arms counters, tells peers the parity slot is free)
 
