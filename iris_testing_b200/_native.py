@@ -99,6 +99,7 @@ class GemmArgs(C.Structure):
         ("single_group_rows", C.c_int),
         ("mma_n", C.c_int),
         ("cta_pair", C.c_int),
+        ("a_base", C.c_void_p),
     ]
 
 

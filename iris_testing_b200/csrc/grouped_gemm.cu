@@ -371,6 +371,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
             }
           }
         }
+        if constexpr (EPI == B200_EPI_ROUTER) {
+          // The router streams its activations once, in 128-byte pieces 2*K bytes apart (one
+          // piece per row and k-block): poor DRAM page locality.  The rows of a tile are one
+          // contiguous region, so ask L2 for it up front in large sequential requests; the
+          // tiled loads below then hit L2.
+          if (ga.a_base != nullptr) {
+            const int rows_here = min(BM, c.g_rows[g] - half0);
+            const size_t row_bytes = static_cast<size_t>(ga.K) * 2;
+            const char* base = static_cast<const char*>(ga.a_base) + static_cast<size_t>(row0) * row_bytes;
+            const size_t total = static_cast<size_t>(max(rows_here, 0)) * row_bytes;
+            for (size_t off = 0; off < total; off += 32768)
+              l2_prefetch_bulk(base + off, static_cast<uint32_t>(min(static_cast<size_t>(32768), total - off)));
+          }
+        }
         const int brow = g * ga.N + n * BN + static_cast<int>(cta_rank) * S::B_ROWS;
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&c.empty[stage], phase ^ 1u, w, ST_TIMEOUT_PIPE_EMPTY)) { ok = false; break; }
@@ -382,7 +396,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
             tma_load_2d_pair(sa, &tmap_a, lead_bar, kb * BK, row0);
             tma_load_2d_pair(sa + A_STAGE_BYTES, &tmap_b, lead_bar, kb * BK, brow);
           } else {
-            mbar_expect_tx(&c.full[stage], STAGE_BYTES);
+            // the router's weight box holds only mma_n rows (the host encodes its map that way)
+            const uint32_t tx = (EPI == B200_EPI_ROUTER && ga.mma_n > 0)
+                                    ? static_cast<uint32_t>(A_STAGE_BYTES + ga.mma_n * BK * 2)
+                                    : static_cast<uint32_t>(STAGE_BYTES);
+            mbar_expect_tx(&c.full[stage], tx);
             tma_load_2d(sa, &tmap_a, &c.full[stage], kb * BK, row0);
             tma_load_2d(sa + A_STAGE_BYTES, &tmap_b, &c.full[stage], kb * BK, brow);
           }
@@ -818,8 +836,9 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
                        : a;
   r = make_tmap_bf16(&ta1, a1, a_rows, ga->K, BM);
   if (r != 0) return r;
-  r = make_tmap_bf16(&tb, w, static_cast<long long>(G) * ga->N, ga->K,
-                     (ga->cta_pair != 0 && num_ctas >= 2) ? BN / 2 : BN);
+  int b_box = (ga->cta_pair != 0 && num_ctas >= 2) ? BN / 2 : BN;
+  if (epi == B200_EPI_ROUTER && ga->mma_n > 0) b_box = ga->mma_n;   // few experts: a short weight box
+  r = make_tmap_bf16(&tb, w, static_cast<long long>(G) * ga->N, ga->K, b_box);
   if (r != 0) return r - 10;
   b200_dispatch_args dz;
   b200_combine_args cz;

@@ -79,6 +79,8 @@ typedef struct {
   int single_group_rows;          // used when group_rows is null: one group of this many rows
   int mma_n;                      // N of the MMA instruction (multiple of 16, <= 256); 0 = 256
   int cta_pair;                   // 1: two CTAs per MMA (cta_group::2, 256-row tiles)
+  const void* a_base;             // activation buffer (same memory the A tensor map covers); used by
+                                  // the router build to prefetch whole rows into L2
 } b200_gemm_args;
 
 // Router epilogue: the accumulator row holds the logits of one token.

@@ -88,6 +88,7 @@ def _router_tensor_core(x, wr_kmajor, bias, topk, renormalize, idx, w, status=No
     ga.group_rows = None
     ga.single_group_rows = T
     ga.mma_n = max(16, (E + 15) // 16 * 16)
+    ga.a_base = x.data_ptr()           # lets the kernel prefetch whole token rows into L2
     ga.status = status.data_ptr()
     ga.wait_budget_ns = int(2e9)
     ra = nv.RouterArgs()
