@@ -58,20 +58,23 @@ def router_topk(x: torch.Tensor, w_router: torch.Tensor, topk: int,
     return (idx, w, logits) if return_logits else (idx, w)
 
 
-_KMAJOR_CACHE = {}
-
-
 def router_kmajor(w_router: torch.Tensor) -> torch.Tensor:
-    """[D, E] -> contiguous [E, D] (the layout the tensor-core router reads), cached per
-    (storage, version) so that an unchanged parameter is transposed once."""
-    key = (w_router.data_ptr(), tuple(w_router.shape), w_router._version)
-    hit = _KMAJOR_CACHE.get(key)
-    if hit is None:
-        if len(_KMAJOR_CACHE) > 64:
-            _KMAJOR_CACHE.clear()
-        hit = w_router.t().contiguous()
-        _KMAJOR_CACHE[key] = hit
-    return hit
+    """[D, E] -> contiguous [E, D] (the layout the tensor-core router reads).
+
+    The transposed copy is cached on the tensor object itself together with the tensor's
+    version counter, so an unchanged parameter is transposed once, an in-place update
+    refreshes it, and the cache cannot outlive the tensor (an address-keyed cache would hand
+    a new tensor that reuses freed memory somebody else's transposed weights)."""
+    ver = w_router._version
+    hit = getattr(w_router, "_b200_kmajor", None)
+    if hit is not None and hit[0] == ver and hit[1].device == w_router.device:
+        return hit[1]
+    t = w_router.detach().t().contiguous()
+    try:
+        w_router._b200_kmajor = (ver, t)
+    except AttributeError:      # exotic tensor subclasses without a __dict__: just do not cache
+        pass
+    return t
 
 
 def _router_tensor_core(x, wr_kmajor, bias, topk, renormalize, idx, w, status=None) -> None:

@@ -191,3 +191,16 @@ def test_capacity_and_heap_sizing():
     need = heap_bytes_needed(cfg, 16384)
     assert need > 2 * worst * 4096 * 2                           # two parity copies of the receive buffer
     assert heap_bytes_needed(cfg, 16384, cap_rows=1024) < need
+
+
+def test_router_weight_cache_follows_the_tensor_not_its_address():
+    from iris_testing_b200.ops.router import router_kmajor
+    w = torch.randn(16, 4)
+    t = router_kmajor(w)
+    assert router_kmajor(w) is t and torch.equal(t, w.t())
+    w.mul_(2.0)                                   # in-place update: version changes
+    assert torch.equal(router_kmajor(w), w.t())
+    ptr = w.data_ptr()
+    del w, t
+    w2 = torch.randn(16, 4)                       # may reuse the freed block
+    assert torch.equal(router_kmajor(w2), w2.t()), (ptr, w2.data_ptr())
