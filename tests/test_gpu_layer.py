@@ -44,6 +44,11 @@ def test_fused_layer_matches_dense_reference(D, F, E, k, gated, T, pair):
     y_short = layer(x[: T // 2])                        # fewer tokens than max_tokens
     assert torch.allclose(y_short.float(), ref[: T // 2], atol=3e-2 * float(ref.abs().max()), rtol=3e-2)
     layer.check_status()
+    y_none = layer(x[:0])                               # a rank with no tokens still takes part
+    assert y_none.shape == (0, cfg.out_dim)
+    y_again = layer(x[: T // 2])
+    assert torch.equal(y_again, y_short)                # deterministic, and state survived the empty step
+    layer.check_status()
 
 
 def test_fused_layer_skewed_routing_and_empty_experts():
