@@ -15,6 +15,8 @@ the device instead of a host clock around prints and a host barrier.
             weighted sum are included on both sides.
 * ``layer`` the fused MoE layer (router + dispatch + experts + combine) vs the same layer
             on library collectives (``AllToAllMoEBaseline``); needs ``FFN`` (0 = single Linear).
+            ``TRACE=1`` adds one JSON line per rank: device time of each phase and when
+            (relative to the fused kernel's start) the received tiles became usable.
 
 Launch: ``python benchmark.py`` spawns ``WORLD_SIZE`` processes (one per GPU); under
 ``torch.distributed.run`` it uses the ranks it is given.  One JSON line per run is printed
@@ -258,6 +260,18 @@ def run_layer(rank: int, world: int, dev: torch.device) -> None:
     ours = max_rank_mean(timed(lambda: layer(x)), dev)
     lib = max_rank_mean(timed(lambda: base.forward(x)), dev)
     layer.check_status()
+    if env_int("TRACE", 0):
+        # per-rank overlap evidence: phase times and when received tiles became usable
+        layer.profile = True
+        layer.trace_arrivals = True
+        if world > 1:
+            dist.barrier()
+        layer(x)
+        phases = {k: round(v) for k, v in layer.phase_times_us().items()}
+        arrivals = {k: (round(v, 1) if isinstance(v, float) else v) for k, v in layer.arrival_report().items()}
+        layer.profile = layer.trace_arrivals = False
+        print(json.dumps(dict(rank=rank, rows=int(layer.group_rows.sum().item()), phases_us=phases,
+                              arrivals=arrivals)), flush=True)
     rows = int(layer.group_rows.sum().item())
     rows_max = int(allreduce_max(torch.tensor([rows], device=dev)).item())
     flops = 2.0 * rows_max * D * (3 * F if F > 0 else cfg.out_dim)
