@@ -196,6 +196,11 @@ def run_ours(args) -> None:
     # ---- device-timed region
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     fence(world)
+    import ctypes
+    from iris_testing_b200 import _native
+    count_fn = _native.lib().b200_launch_count      # incremented by every native launcher
+    count_fn.restype = ctypes.c_longlong
+    launches_before = count_fn()
     sampler.mark_begin()
     e0.record()
     for i in range(args.steps):
@@ -203,6 +208,7 @@ def run_ours(args) -> None:
     e1.record()
     fence(world)
     sampler.mark_end()
+    launches = int(count_fn() - launches_before)
     us = e0.elapsed_time(e1) * 1000.0 / args.steps
     clocks = sampler.stop()
     layer.check_status()
@@ -262,7 +268,7 @@ def run_ours(args) -> None:
     e2e = {"value": round(e2e_us, 2), "unit": "us",
            "h2d_bytes_per_step": T * cfg.hidden_dim * 2, "d2h_bytes_per_step": 4,
            "api": "iris_testing_b200.models.MoELayer.forward"}
-    launches = layer.launches_per_forward * args.steps
+    assert launches == layer.launches_per_forward * args.steps, (launches, layer.launches_per_forward)
     emit(args, rank, world, us, e2e, launches, clocks,
          dict(timed="router + plan + dispatch + expert MLP + combine (5 kernels' worth, 6 launches)",
               capacity_rows=layer.cap_rows), "ours")

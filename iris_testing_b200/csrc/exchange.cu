@@ -378,6 +378,7 @@ int b200_padded_dispatch(const void* payload, const int* send_counts, const int*
       static_cast<const uint4*>(payload), send_counts, dst_offsets, make_table(peer_pca, world),
       make_table(peer_token_buf, world), make_table(peer_counts_ready, world),
       make_table(peer_token_sync, world), rank, world, e_local, cap, hidden_dim / 8, block_m, status);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -389,6 +390,7 @@ int b200_padded_return(const void* out_buf, const int* pca, const unsigned long 
   b200::padded_return_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(out_buf), pca, make_table(peer_ret_buf, world),
       make_table(peer_ret_sync, world), rank, world, e_local, cap, hidden_dim / 8, block_m);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -405,6 +407,7 @@ int b200_weighted_gather(const void* ret_buf, const int* dst_slot, const int* to
       static_cast<const __nv_bfloat16*>(ret_buf), dst_slot, topk_idx, bucket_start, topk_w,
       static_cast<const uint32_t*>(ret_sync), send_counts, T, topk, world, e_local, cap, hidden_dim,
       block_m, static_cast<__nv_bfloat16*>(y), status, budget_ns);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -417,6 +420,7 @@ int b200_shuffle(void* token_buf, void* packed, const int* pca, const void* coun
       static_cast<uint4*>(token_buf), static_cast<uint4*>(packed), pca,
       static_cast<const uint32_t*>(counts_ready), static_cast<const uint32_t*>(token_sync), world,
       e_local, cap, hidden_dim / 8, block_m, wait, inverse, group_rows, status, budget_ns);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -431,6 +435,7 @@ int b200_slot_reduce(const void* out_slots, const int* dst_slot, void* arrived, 
   b200::slot_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(out_slots), dst_slot, static_cast<uint32_t*>(arrived), expected, T,
       topk, hidden_dim, static_cast<__nv_bfloat16*>(y), *ra, status, budget_ns);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -443,6 +448,7 @@ int b200_silu_gate(const void* gate, const void* up, void* out, long long n, voi
   b200::silu_gate_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat162*>(gate), static_cast<const __nv_bfloat162*>(up),
       static_cast<__nv_bfloat162*>(out), static_cast<size_t>(n2));
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -452,6 +458,7 @@ int b200_barrier(const unsigned long long* peer_flags, void* local_flags, int ra
   b200::barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
       make_table(peer_flags, world), static_cast<uint32_t*>(local_flags), rank, world, epoch, status,
       budget_ns);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -799,6 +799,7 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta1, const C
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  b200_count_launches(1);
   return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, ta1, tb, ga, da, ca, ra));
 }
 

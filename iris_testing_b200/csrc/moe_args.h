@@ -93,6 +93,11 @@ typedef struct {
   float* topk_w;                  // [rows, k]
 } b200_router_args;
 
+// Launch accounting: every host launcher adds the kernels it launched; a benchmark reads the
+// counter before and after its timed region.
+void b200_count_launches(int n);
+long long b200_launch_count(void);
+
 #ifdef __cplusplus
 }
 #endif

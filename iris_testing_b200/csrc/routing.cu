@@ -238,6 +238,7 @@ int b200_router_topk_simple(const void* x, const void* wr, const float* bias, in
                                     warps * E * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(wr), bias, T, D, E, k,
       renorm, topk_idx, topk_w, logits_out);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -250,6 +251,7 @@ int b200_plan(const int* topk_idx, int n_flat, int num_experts, int* rank_in_buc
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   b200::plan_rank_kernel<<<num_experts, 1024, 0, st>>>(topk_idx, n_flat, num_experts, rank_in_bucket,
                                                        counts);
+  b200_count_launches(1);
   b200::PlanPushArgs pz;
   memset(&pz, 0, sizeof(pz));
   int blocks = (n_flat + 255) / 256;
@@ -258,6 +260,7 @@ int b200_plan(const int* topk_idx, int n_flat, int num_experts, int* rank_in_buc
   b200::plan_finalize_kernel<<<blocks, 256, 0, st>>>(topk_idx, rank_in_bucket, counts, n_flat,
                                                      num_experts, bucket_start, send_order, dst_slot,
                                                      push ? *push : pz, push ? 1 : 0);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -270,6 +273,7 @@ int b200_pack_rows(const void* x, const int* send_order, int n_flat, int topk, i
   b200::pack_rows_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(x), send_order, n_flat, topk, hidden_dim / 8,
       static_cast<uint4*>(payload));
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -316,6 +320,7 @@ int b200_plan_noalloc(const int* topk_idx, int n_flat, int num_experts, int* cou
   int* scratch = b200::g_plan_scratch_addr[dev];
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   b200::plan_rank_kernel<<<num_experts, 1024, 0, st>>>(topk_idx, n_flat, num_experts, scratch, counts);
+  b200_count_launches(1);
   b200::PlanPushArgs pz;
   memset(&pz, 0, sizeof(pz));
   int blocks = (n_flat + 255) / 256;
@@ -323,6 +328,7 @@ int b200_plan_noalloc(const int* topk_idx, int n_flat, int num_experts, int* cou
   if (blocks > 1184) blocks = 1184;
   b200::plan_finalize_kernel<<<blocks, 256, 0, st>>>(topk_idx, scratch, counts, n_flat, num_experts,
                                                      bucket_start, send_order, dst_slot, pz, 0);
+  b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
 

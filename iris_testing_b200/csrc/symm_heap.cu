@@ -12,6 +12,12 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <atomic>
+
+#include "moe_args.h"
+
+static std::atomic<long long> g_launches{0};
+
 extern "C" {
 
 // Allocates `bytes` of device memory on `device`, zero-filled.
@@ -61,6 +67,9 @@ int b200_heap_close(int device, void* mapped) {
 int b200_memset_async(void* ptr, int value, unsigned long long bytes, void* stream) {
   return static_cast<int>(cudaMemsetAsync(ptr, value, bytes, static_cast<cudaStream_t>(stream)));
 }
+
+void b200_count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 const char* b200_error_string(int code) {
   return cudaGetErrorString(static_cast<cudaError_t>(code));
