@@ -42,7 +42,7 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     a          [M, K] bf16, groups packed back to back
     w_kmajor   [G, N, K] bf16
     group_rows int32 [G] on the device (rows per group; sum <= M)
-    group_m    M-tiles per L2-blocking chunk; 0 picks about 24 MB of activations per chunk.
+    group_m    M-tiles per L2-blocking chunk; 0 picks about 48 MB of activations per chunk.
     cta_pair   True: two CTAs per MMA (tcgen05 cta_group::2, 256-row tiles); None picks it
                when the groups average at least 256 rows.
     epilogue   EPI_STORE -> out [M, N];  EPI_SILU_GATE -> out [M, N/2] where every
