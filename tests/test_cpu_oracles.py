@@ -204,3 +204,23 @@ def test_router_weight_cache_follows_the_tensor_not_its_address():
     del w, t
     w2 = torch.randn(16, 4)                       # may reuse the freed block
     assert torch.equal(router_kmajor(w2), w2.t()), (ptr, w2.data_ptr())
+
+
+def test_reference_module_names_are_importable():
+    from iris_testing_b200.compat.baseline import (BaselineBuffers, init_baseline_buffers,
+                                                   reorder_flat_to_token_buf, run_baseline_ref)
+    from iris_testing_b200.compat.layers.all_to_all import custom_a2a as a2a
+    from iris_testing_b200.compat.layers.expert import expert as ex
+    from iris_testing_b200.compat.layers.token_shuffle import shuffle as sh
+    from iris_testing_b200.compat.utils import gen_local_tokens as glt, route_and_pack_padding_free as rp
+    assert all(callable(f) for f in (a2a, ex, sh, glt, rp, run_baseline_ref, reorder_flat_to_token_buf))
+    # single-process run of the baseline runner with the reference's argument list
+    x = glt(1, 16, 8, torch.float32, "cpu", 0, 0)
+    router = gen_router(8, 4, torch.float32, "cpu", 0, std=None)
+    payload, counts, _, _ = rp(x, router, 2, 1, 4)
+    bufs = init_baseline_buffers(1, 4, 32, 8, torch.float32, "cpu", int(counts.sum()), allocate_token_buf=True)
+    assert isinstance(bufs, BaselineBuffers)
+    tb, timings, meta = run_baseline_ref(0, 1, 4, 32, 8, payload, counts, bufs, do_reorder=True, barrier=False)
+    assert tb.shape == (4, 1, 32, 8) and set(timings) == {"step1_ms", "step2_ms", "reorder_ms"}
+    assert meta["total_send"] == meta["total_recv"] == int(counts.sum())
+    assert torch.equal(tb[0, 0, :int(counts[0, 0])], payload[:int(counts[0, 0])])
