@@ -100,7 +100,7 @@ struct Geo {
 // group in chunks of `gm` M-tiles; inside a chunk the M index runs fastest so
 // that concurrently running CTAs share a few weight tiles and a chunk of A
 // that stays resident in L2 while the N index sweeps.
-__device__ __forceinline__ bool decode_tile(const ControlSmem& c, int G, int TN, int gm, int idx,
+__host__ __device__ __forceinline__ bool decode_tile(const ControlSmem& c, int G, int TN, int gm, int idx,
                                             int& cursor, int& g, int& m, int& n) {
   while (cursor < G && idx >= TN * c.g_sched_start[cursor + 1]) ++cursor;
   if (cursor >= G) return false;
@@ -113,7 +113,7 @@ __device__ __forceinline__ bool decode_tile(const ControlSmem& c, int G, int TN,
   const int chunk_tiles = gm * TN;
   const int ch = j / chunk_tiles;
   const int r = j - ch * chunk_tiles;
-  const int cm = min(gm, tm - ch * gm);
+  const int cm = (gm < tm - ch * gm) ? gm : (tm - ch * gm);
   n = r / cm;
   m = ch * gm + (r - n * cm);
   return true;
@@ -155,48 +155,65 @@ __device__ __forceinline__ void scan_groups(ControlSmem& c, int G, int lane, int
 
 __device__ __forceinline__ float silu_f(float g) { return g * __frcp_rn(1.0f + __expf(-g)); }
 
+// Reads a routing count.  On the device the table is written by peers, so it is read
+// through L2; the host build of these helpers (index-arithmetic tests) reads plain memory.
+__host__ __device__ __forceinline__ int load_count(const int* p) {
+#ifdef __CUDA_ARCH__
+  return __ldcg(p);
+#else
+  return *p;
+#endif
+}
+
+// Rows this rank receives for local expert e: sum over sources of counts_all[src][me][e].
+__host__ __device__ __forceinline__ int received_rows(const int* cnt, int W, int EL, int me, int e) {
+  int rows = 0;
+  for (int s = 0; s < W; ++s) rows += load_count(cnt + ((s * W + me) * EL + e));
+  return rows;
+}
+
+// Fills sender-table entry `bi` of rank `me` from counts_all[src][dst][e]; returns false when
+// the bucket would overrun the destination's receive capacity.
+// Buckets are visited expert-major, and inside an expert destination-rotated starting with this
+// rank: every rank's expert 0 fills first, each from its nearest "upstream" ranks first.  The
+// receive layout orders the source segments of an expert the same way (self, self-1, self-2,
+// ... modulo the world), so rows land in the order the consumer's M-tiles need them.
+__host__ __device__ __forceinline__ bool fill_bucket(ControlSmem& c, const int* cnt, int W, int EL,
+                                                     int me, int bi, int cap_rows) {
+  const int ET = W * EL;
+  const int e = bi / W, r = bi - e * W;
+  const int dst = (me + r) % W;
+  const int ge = dst * EL + e;
+  const int n = load_count(cnt + ((me * W + dst) * EL + e));
+  int send_start = 0;
+  for (int q = 0; q < ge; ++q) send_start += load_count(cnt + (me * ET + q));
+  int group_start = 0, mtile0 = 0;
+  for (int e2 = 0; e2 < e; ++e2) {
+    const int rows = received_rows(cnt, W, EL, dst, e2);
+    group_start += rows;
+    mtile0 += (rows + BM - 1) / BM;
+  }
+  int within = 0;   // rows of the sources that precede this rank in dst's segment order
+  for (int q = 0; q < r; ++q) within += load_count(cnt + ((((dst - q + W) % W) * W + dst) * EL + e));
+  c.b_count[bi] = n;
+  c.b_send_start[bi] = send_start;
+  c.b_dst_row[bi] = group_start + within;
+  c.b_dst_rel0[bi] = within;
+  c.b_dst_mtile0[bi] = mtile0;
+  c.b_dst_rank[bi] = dst;
+  // units are (bucket, aligned block of SEND_ROWS destination rows); stored un-scanned for now
+  c.b_unit_start[bi + 1] = (n > 0) ? ((within + n - 1) / SEND_ROWS - within / SEND_ROWS + 1) : 0;
+  return !(n > 0 && group_start + within + n > cap_rows) && n >= 0;
+}
+
 // Builds the sender tables and this rank's group sizes from the all-ranks
 // routing counts (counts_all[src][dst][e]).  Runs on every thread of the CTA.
 __device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200_dispatch_args& d,
                                                       int tid, int nthreads, WaitCtx& w) {
   const int W = d.world, EL = d.e_local, ET = W * EL, me = d.rank;
-  const int* cnt = d.counts_all;
-  // rows this rank receives per local expert
-  for (int e = tid; e < EL; e += nthreads) {
-    int rows = 0;
-    for (int s = 0; s < W; ++s) rows += __ldcg(cnt + ((s * W + me) * EL + e));
-    c.g_rows[e] = rows;
-  }
-  // Buckets are visited expert-major, and inside an expert destination-rotated starting
-  // with this rank: every rank's expert 0 fills first, each from its nearest "upstream"
-  // ranks first.  The receive layout orders the source segments of an expert the same
-  // way (self, self-1, self-2, ... modulo the world), so rows land in the order the
-  // consumer's M-tiles need them.
+  for (int e = tid; e < EL; e += nthreads) c.g_rows[e] = received_rows(d.counts_all, W, EL, me, e);
   for (int bi = tid; bi < ET; bi += nthreads) {
-    const int e = bi / W, r = bi - e * W;
-    const int dst = (me + r) % W;
-    const int ge = dst * EL + e;
-    const int n = __ldcg(cnt + ((me * W + dst) * EL + e));
-    int send_start = 0;
-    for (int q = 0; q < ge; ++q) send_start += __ldcg(cnt + (me * ET + q));
-    int group_start = 0, mtile0 = 0;
-    for (int e2 = 0; e2 < e; ++e2) {
-      int rows = 0;
-      for (int s = 0; s < W; ++s) rows += __ldcg(cnt + ((s * W + dst) * EL + e2));
-      group_start += rows;
-      mtile0 += (rows + BM - 1) / BM;
-    }
-    int within = 0;   // rows of the sources that precede this rank in dst's segment order
-    for (int q = 0; q < r; ++q) within += __ldcg(cnt + ((((dst - q + W) % W) * W + dst) * EL + e));
-    c.b_count[bi] = n;
-    c.b_send_start[bi] = send_start;
-    c.b_dst_row[bi] = group_start + within;
-    c.b_dst_rel0[bi] = within;
-    c.b_dst_mtile0[bi] = mtile0;
-    c.b_dst_rank[bi] = dst;
-    // units are (bucket, aligned block of SEND_ROWS destination rows); stored un-scanned for now
-    c.b_unit_start[bi + 1] = (n > 0) ? ((within + n - 1) / SEND_ROWS - within / SEND_ROWS + 1) : 0;
-    if (n > 0 && (group_start + within + n > d.cap_rows || n < 0)) {
+    if (!fill_bucket(c, d.counts_all, W, EL, me, bi, d.cap_rows)) {
       report_status(w.status, ST_OVERFLOW);
       *w.abort_flag = 1;
     }
@@ -899,4 +916,65 @@ extern "C" void b200_abi_sizes_gemm(int* out) {
   out[1] = static_cast<int>(sizeof(b200_dispatch_args));
   out[2] = static_cast<int>(sizeof(b200_combine_args));
   out[3] = static_cast<int>(sizeof(b200_router_args));
+}
+
+// ---------------------------------------------------------------------------
+// Host builds of the index arithmetic above, for tests that check tile coverage and the
+// cross-rank row layout without a GPU.  They run the same decode_tile / fill_bucket code.
+// ---------------------------------------------------------------------------
+extern "C" int b200_debug_tile_order(const int* group_rows, int G, int TN, int group_m, int tile_rows,
+                                     int* out_gmn, int max_tiles) {
+  using namespace b200;
+  if (G < 1 || G > B200_MAX_GROUPS || TN < 1 || group_m < 1 || (tile_rows != BM && tile_rows != 2 * BM))
+    return -1;
+  ControlSmem* c = new ControlSmem();
+  int rows_acc = 0, sched_acc = 0, mt_acc = 0;
+  for (int g = 0; g < G; ++g) {
+    const int r = group_rows[g] < 0 ? 0 : group_rows[g];
+    c->g_rows[g] = r;
+    c->g_row_start[g] = rows_acc;
+    c->g_mtile_start[g] = mt_acc;
+    c->g_sched_start[g] = sched_acc;
+    rows_acc += r;
+    mt_acc += (r + BM - 1) / BM;
+    sched_acc += (r + tile_rows - 1) / tile_rows;
+  }
+  c->g_row_start[G] = rows_acc;
+  c->g_mtile_start[G] = mt_acc;
+  c->g_sched_start[G] = sched_acc;
+  c->total_sched = sched_acc;
+  const int total = sched_acc * TN;
+  int cursor = 0, written = 0;
+  for (int idx = 0; idx < total && written < max_tiles; ++idx, ++written) {
+    int g, m, n;
+    if (!decode_tile(*c, G, TN, group_m, idx, cursor, g, m, n)) break;
+    out_gmn[3 * written + 0] = g;
+    out_gmn[3 * written + 1] = m;
+    out_gmn[3 * written + 2] = n;
+  }
+  delete c;
+  return written == total ? total : -2;
+}
+
+// tables: [7][world * e_local] = count, send_start, dst_row, dst_rel0, dst_mtile0, dst_rank, units
+extern "C" int b200_debug_dispatch_tables(const int* counts_all, int world, int e_local, int rank,
+                                          int cap_rows, int* g_rows, int* tables) {
+  using namespace b200;
+  const int ET = world * e_local;
+  if (world < 1 || world > B200_MAX_WORLD || ET > B200_MAX_EXPERTS || rank < 0 || rank >= world) return -1;
+  ControlSmem* c = new ControlSmem();
+  int ok = 1;
+  for (int e = 0; e < e_local; ++e) g_rows[e] = received_rows(counts_all, world, e_local, rank, e);
+  for (int bi = 0; bi < ET; ++bi) {
+    if (!fill_bucket(*c, counts_all, world, e_local, rank, bi, cap_rows)) ok = 0;
+    tables[0 * ET + bi] = c->b_count[bi];
+    tables[1 * ET + bi] = c->b_send_start[bi];
+    tables[2 * ET + bi] = c->b_dst_row[bi];
+    tables[3 * ET + bi] = c->b_dst_rel0[bi];
+    tables[4 * ET + bi] = c->b_dst_mtile0[bi];
+    tables[5 * ET + bi] = c->b_dst_rank[bi];
+    tables[6 * ET + bi] = c->b_unit_start[bi + 1];
+  }
+  delete c;
+  return ok;
 }
