@@ -3,7 +3,7 @@ kernels; CPU tensors run the PyTorch restatements in :mod:`.cpu_ref`."""
 from . import cpu_ref
 from .activation import silu_gate
 from .combine import padded_return, weighted_gather
-from .dispatch import AllToAllOp, custom_a2a
+from .dispatch import AllToAllOp, custom_a2a, zero_padding
 from .expert import Expert, expert, grouped_gemm, to_kmajor
 from .plan import Plan, make_plan, pack_rows
 from .router import router_topk

@@ -108,3 +108,18 @@ class AllToAllOp(torch.autograd.Function):
 
 
 custom_a2a = AllToAllOp.apply
+
+
+def zero_padding(token_buf: torch.Tensor, pca: torch.Tensor) -> torch.Tensor:
+    """Zero every padding row ``token_buf[e, src, m >= pca[e, src]]`` in place.
+
+    The dispatch transfers valid rows only (as the reference does, kernels.py:104), so a
+    reused buffer keeps stale rows from an earlier, larger message in its padding.  Call this
+    after the dispatch has landed when the consumer reads the padded layout directly; the
+    shuffle and the grouped GEMM never look at padding rows.  Plain tensor ops, any device."""
+    cap = token_buf.shape[2]
+    m = torch.arange(cap, device=token_buf.device).view(1, 1, cap)
+    pad = m >= pca.to(token_buf.device).unsqueeze(-1)
+    token_buf.masked_fill_(pad.unsqueeze(-1), 0)
+    return token_buf
+

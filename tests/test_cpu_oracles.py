@@ -224,3 +224,14 @@ def test_reference_module_names_are_importable():
     assert tb.shape == (4, 1, 32, 8) and set(timings) == {"step1_ms", "step2_ms", "reorder_ms"}
     assert meta["total_send"] == meta["total_recv"] == int(counts.sum())
     assert torch.equal(tb[0, 0, :int(counts[0, 0])], payload[:int(counts[0, 0])])
+
+
+def test_zero_padding_clears_stale_rows_only():
+    from iris_testing_b200.ops import zero_padding
+    buf = torch.ones(2, 3, 4, 5)
+    pca = torch.tensor([[0, 4, 2], [1, 3, 0]], dtype=torch.int32)
+    zero_padding(buf, pca)
+    for e in range(2):
+        for s_ in range(3):
+            n = int(pca[e, s_])
+            assert bool((buf[e, s_, :n] == 1).all()) and bool((buf[e, s_, n:] == 0).all())
