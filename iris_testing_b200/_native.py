@@ -55,6 +55,7 @@ class DispatchArgs(C.Structure):
         ("counts_flag", C.c_void_p),
         ("epoch", C.c_uint32),
         ("cap_rows", C.c_int),
+        ("cap_mtiles", C.c_int),
         ("drop_signal", C.c_int),
         ("peer_recv", C.c_ulonglong * MAX_WORLD),
         ("peer_meta", C.c_ulonglong * MAX_WORLD),
@@ -100,6 +101,9 @@ class GemmArgs(C.Structure):
         ("mma_n", C.c_int),
         ("cta_pair", C.c_int),
         ("a_base", C.c_void_p),
+        ("a_rows", C.c_longlong),
+        ("l2_hints", C.c_int),
+        ("tma_store", C.c_int),
     ]
 
 

@@ -191,7 +191,8 @@ __global__ void weighted_gather_kernel(const __nv_bfloat16* __restrict__ ret_buf
 __global__ void shuffle_kernel(uint4* token_buf, uint4* packed, const int* pca,
                                const uint32_t* counts_ready, const uint32_t* token_sync, int world,
                                int e_local, int cap, int row16, int block_m, int wait, int inverse,
-                               int* group_rows, int* status, unsigned long long budget_ns) {
+                               int* group_rows, int max_rows, int* status,
+                               unsigned long long budget_ns) {
   __shared__ int s_off[B200_MAX_EXPERTS + 1];   // e_local * world cells
   __shared__ int s_abort;
   const int cells = e_local * world;
@@ -221,7 +222,12 @@ __global__ void shuffle_kernel(uint4* token_buf, uint4* packed, const int* pca,
       group_rows[e] = s_off[(e + 1) * world] - s_off[e * world];
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  const int total = s_off[cells];
+  // the packed buffer holds max_rows rows: more valid rows than that are reported, not copied
+  if (s_off[cells] > max_rows && blockIdx.x == 0 && threadIdx.x == 0) {
+    report_status(status, ST_OVERFLOW);
+    if (status != nullptr) atomicMax(status + 1, s_off[cells]);
+  }
+  const int total = min(s_off[cells], max_rows);
   int cell = 0;
   for (int r = warp; r < total; r += nwarps) {
     while (r >= s_off[cell + 1]) ++cell;
@@ -253,6 +259,7 @@ struct RetireArgs {
   unsigned long long stride_ready;   // bytes between the two parity copies of ready_counters
 };
 
+template <int KMAX>   // topk <= KMAX; about eight 16-byte loads per lane are kept in flight
 __global__ void slot_reduce_kernel(const __nv_bfloat16* out_slots, const int* __restrict__ dst_slot,
                                    uint32_t* arrived, uint32_t expected, int T, int topk, int H,
                                    __nv_bfloat16* __restrict__ y, RetireArgs ra, int* status,
@@ -260,36 +267,63 @@ __global__ void slot_reduce_kernel(const __nv_bfloat16* out_slots, const int* __
   __shared__ int s_abort;
   if (threadIdx.x == 0) {
     s_abort = 0;
-    WaitCtx w; w.abort_flag = &s_abort; w.status = status; w.budget_ns = budget_ns;
-    wait_flag_geq(arrived, expected, w, ST_TIMEOUT_COMBINE);
+    // A kernel of this step has already reported an error on this rank: its rows will never
+    // arrive, so do not wait for them (the iteration is still retired below).
+    if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) {
+      s_abort = 1;
+    } else {
+      WaitCtx w; w.abort_flag = &s_abort; w.status = status; w.budget_ns = budget_ns;
+      wait_flag_geq(arrived, expected, w, ST_TIMEOUT_COMBINE);
+    }
   }
   __syncthreads();
   if (!s_abort) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int nwarps = (gridDim.x * blockDim.x) >> 5;
+    constexpr int U = 8 / KMAX;    // 16-byte column chunks per lane in flight at once (times topk loads)
     for (int t = warp; t < T; t += nwarps) {
-      for (int c0 = lane * 8; c0 < H; c0 += 256) {
-        float acc[8];
+      // results sit at the row's position in the packed send order (dst_slot), or at
+      // t*topk+s when no map is given
+      size_t row[KMAX];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int s = 0; s < topk; ++s) {
-          // results sit at the row's position in the packed send order (dst_slot), or at
-          // t*topk+s when no map is given
-          const size_t row = dst_slot != nullptr ? static_cast<size_t>(__ldg(dst_slot + t * topk + s))
-                                                 : static_cast<size_t>(t) * topk + s;
-          const uint4 v = ld_16(reinterpret_cast<const uint4*>(out_slots + row * H + c0));
-          const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+      for (int s = 0; s < KMAX; ++s)
+        if (s < topk)
+          row[s] = dst_slot != nullptr ? static_cast<size_t>(__ldg(dst_slot + t * topk + s))
+                                       : static_cast<size_t>(t) * topk + s;
+      for (int cb = lane * 8; cb < H; cb += 256 * U) {
+        uint4 v[U][KMAX];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float2 f = __bfloat1622float2(h2[j]);
-            acc[2 * j] += f.x;
-            acc[2 * j + 1] += f.y;
-          }
+        for (int u = 0; u < U; ++u) {
+          const int c0 = cb + u * 256;
+#pragma unroll
+          for (int s = 0; s < KMAX; ++s)
+            if (s < topk && c0 < H)
+              v[u][s] = ld_16(reinterpret_cast<const uint4*>(out_slots + row[s] * H + c0));
         }
-        uint4 o;
-        o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
-        o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
-        *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * H + c0) = o;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int c0 = cb + u * 256;
+          if (c0 >= H) continue;
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+          for (int s = 0; s < KMAX; ++s) {
+            if (s < topk) {
+              const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&v[u][s]);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __bfloat1622float2(h2[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+              }
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+          o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+          *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * H + c0) = o;
+        }
       }
     }
   }
@@ -413,13 +447,13 @@ int b200_weighted_gather(const void* ret_buf, const int* dst_slot, const int* to
 
 int b200_shuffle(void* token_buf, void* packed, const int* pca, const void* counts_ready,
                  const void* token_sync, int world, int e_local, int cap, int hidden_dim, int block_m,
-                 int wait, int inverse, int* group_rows, int* status, unsigned long long budget_ns,
-                 void* stream) {
-  if (hidden_dim % 8 != 0 || world * e_local > B200_MAX_EXPERTS) return -1;
+                 int wait, int inverse, int* group_rows, int max_rows, int* status,
+                 unsigned long long budget_ns, void* stream) {
+  if (hidden_dim % 8 != 0 || world * e_local > B200_MAX_EXPERTS || max_rows < 0) return -1;
   b200::shuffle_kernel<<<148 * 4, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<uint4*>(token_buf), static_cast<uint4*>(packed), pca,
       static_cast<const uint32_t*>(counts_ready), static_cast<const uint32_t*>(token_sync), world,
-      e_local, cap, hidden_dim / 8, block_m, wait, inverse, group_rows, status, budget_ns);
+      e_local, cap, hidden_dim / 8, block_m, wait, inverse, group_rows, max_rows, status, budget_ns);
   b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
@@ -428,13 +462,23 @@ int b200_slot_reduce(const void* out_slots, const int* dst_slot, void* arrived, 
                      int T, int topk,
                      int hidden_dim, void* y, const b200::RetireArgs* ra, int* status,
                      unsigned long long budget_ns, void* stream) {
-  if (hidden_dim % 8 != 0 || ra == nullptr) return -1;
+  if (hidden_dim % 8 != 0 || ra == nullptr || topk < 1 || topk > 8) return -1;
   int blocks = (T + 7) / 8;
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 4) blocks = 148 * 4;
-  b200::slot_reduce_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(out_slots), dst_slot, static_cast<uint32_t*>(arrived), expected, T,
-      topk, hidden_dim, static_cast<__nv_bfloat16*>(y), *ra, status, budget_ns);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto* os = static_cast<const __nv_bfloat16*>(out_slots);
+  auto* ar = static_cast<uint32_t*>(arrived);
+  auto* yo = static_cast<__nv_bfloat16*>(y);
+  if (topk <= 2)
+    b200::slot_reduce_kernel<2><<<blocks, 256, 0, st>>>(os, dst_slot, ar, expected, T, topk, hidden_dim, yo,
+                                                        *ra, status, budget_ns);
+  else if (topk <= 4)
+    b200::slot_reduce_kernel<4><<<blocks, 256, 0, st>>>(os, dst_slot, ar, expected, T, topk, hidden_dim, yo,
+                                                        *ra, status, budget_ns);
+  else
+    b200::slot_reduce_kernel<8><<<blocks, 256, 0, st>>>(os, dst_slot, ar, expected, T, topk, hidden_dim, yo,
+                                                        *ra, status, budget_ns);
   b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

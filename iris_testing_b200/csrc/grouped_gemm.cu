@@ -48,8 +48,9 @@ constexpr int MAX_STAGES = 6;
 constexpr int UMMA_K = 16;
 constexpr int A_STAGE_BYTES = BM * BK * 2;            // 16 KiB per CTA
 constexpr int STG_COLS = 64;                          // columns per epilogue pass
-constexpr int STG_ROW_BYTES = STG_COLS * 2 + 16;      // padded: conflict-free 16 B stores
-constexpr int STG_BYTES = BM * STG_ROW_BYTES;         // 18 KiB
+constexpr int STG_ROW_BYTES = STG_COLS * 2;           // 128 B rows, 16-byte chunks XOR-swizzled by row
+constexpr int STG_WARP_BYTES = 32 * STG_ROW_BYTES;    // one epilogue warp's 32 x 64 box (a TMA store box)
+constexpr int STG_BYTES = 4 * STG_WARP_BYTES;         // 16 KiB
 constexpr int TMEM_COLS = 512;                        // two 256-column accumulators
 constexpr int NUM_THREADS_PLAIN = 192;
 constexpr int SENDER_WARPS = 4;    // token-sender warps per CTA in the fused-dispatch build
@@ -64,6 +65,7 @@ struct __align__(16) ControlSmem {
   uint64_t drain;
   uint32_t tmem_base;
   int abort_flag;
+  int overflow;       // set during set-up only: this rank neither sends nor computes
   int total_mtiles;
   int total_units;
   int g_rows[B200_MAX_GROUPS];
@@ -155,15 +157,10 @@ __device__ __forceinline__ void scan_groups(ControlSmem& c, int G, int lane, int
 
 __device__ __forceinline__ float silu_f(float g) { return g * __frcp_rn(1.0f + __expf(-g)); }
 
-// Reads a routing count.  On the device the table is written by peers, so it is read
-// through L2; the host build of these helpers (index-arithmetic tests) reads plain memory.
-__host__ __device__ __forceinline__ int load_count(const int* p) {
-#ifdef __CUDA_ARCH__
-  return __ldcg(p);
-#else
-  return *p;
-#endif
-}
+// Reads a routing count.  On the device the table has been staged in shared memory (one
+// coalesced read of the peer-written table per CTA); the host build of these helpers
+// (index-arithmetic tests) reads plain memory.
+__host__ __device__ __forceinline__ int load_count(const int* p) { return *p; }
 
 // Rows this rank receives for local expert e: sum over sources of counts_all[src][me][e].
 __host__ __device__ __forceinline__ int received_rows(const int* cnt, int W, int EL, int me, int e) {
@@ -207,14 +204,16 @@ __host__ __device__ __forceinline__ bool fill_bucket(ControlSmem& c, const int* 
 }
 
 // Builds the sender tables and this rank's group sizes from the all-ranks
-// routing counts (counts_all[src][dst][e]).  Runs on every thread of the CTA.
+// routing counts (`cnt` = counts_all[src][dst][e], staged in shared memory).  Runs on every
+// thread of the CTA.
 __device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200_dispatch_args& d,
-                                                      int tid, int nthreads, WaitCtx& w) {
+                                                      const int* cnt, int tid, int nthreads, WaitCtx& w) {
   const int W = d.world, EL = d.e_local, ET = W * EL, me = d.rank;
-  for (int e = tid; e < EL; e += nthreads) c.g_rows[e] = received_rows(d.counts_all, W, EL, me, e);
+  for (int e = tid; e < EL; e += nthreads) c.g_rows[e] = received_rows(cnt, W, EL, me, e);
   for (int bi = tid; bi < ET; bi += nthreads) {
-    if (!fill_bucket(c, d.counts_all, W, EL, me, bi, d.cap_rows)) {
+    if (!fill_bucket(c, cnt, W, EL, me, bi, d.cap_rows)) {
       report_status(w.status, ST_OVERFLOW);
+      c.overflow = 1;
       *w.abort_flag = 1;
     }
   }
@@ -224,7 +223,8 @@ template <int EPI, bool FUSED, int CG>
 __global__ void __launch_bounds__(FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
                     const __grid_constant__ CUtensorMap tmap_a1,
-                    const __grid_constant__ CUtensorMap tmap_b, const b200_gemm_args ga,
+                    const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_o, const b200_gemm_args ga,
                     const b200_dispatch_args da_in, const b200_combine_args ca_in,
                     const b200_router_args ra) {
   // Per-parity state: the iteration number lives in device memory (when iter_ptr is set), so
@@ -286,6 +286,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   // ---------------------------------------------------------------- set-up
   if (tid == 0) {
     c.abort_flag = 0;
+    c.overflow = 0;
     c.total_units = 0;
     for (int i = 0; i < 64; ++i) c.ready_seen[i] = 0;
     for (int s = 0; s < STAGES; ++s) {
@@ -300,6 +301,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
     fence_mbar_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
+    if (ga.tma_store) tma_prefetch_desc(&tmap_o);
   }
   if (warp == 1) {
     if constexpr (CG == 2) {
@@ -318,7 +320,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
     // every rank's routing counts must have landed before offsets can be built
     if (tid < da.world) wait_flag_geq(da.counts_flag + tid, da.epoch, w, ST_TIMEOUT_COUNTS);
     __syncthreads();
-    if (!c.abort_flag) build_dispatch_tables(c, da, tid, nthreads, w);
+    // One coalesced read of the peer-written table (world * experts ints, at most 4 KiB) into the
+    // still idle epilogue staging buffer; the tables are then built from shared memory.
+    int* cnt_s = reinterpret_cast<int*>(staging);
+    if (!c.abort_flag) {
+      const int ncnt = da.world * da.world * da.e_local;
+      for (int i = tid; i < ncnt; i += nthreads) cnt_s[i] = __ldcg(da.counts_all + i);
+    }
+    __syncthreads();
+    if (!c.abort_flag) build_dispatch_tables(c, da, cnt_s, tid, nthreads, w);
     __syncthreads();
     if (tid == 0) {
       const int ET = da.world * da.e_local;
@@ -344,14 +354,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   __syncthreads();
   tc_fence_after_sync();
 
-  if constexpr (FUSED) {
-    if (tid == 0 && c.g_row_start[G] > da.cap_rows) {
-      report_status(w.status, ST_OVERFLOW);
-      if (w.status != nullptr) atomicMax(w.status + 1, c.g_row_start[G]);   // rows that were needed
-      c.abort_flag = 1;
-    }
-    __syncthreads();
+  // The group sizes come from device memory: when they add up to more rows than the activation
+  // (and output) buffer holds, nothing is sent, computed or stored; the host reads the status.
+  if (tid == 0 && c.g_row_start[G] > (FUSED ? static_cast<long long>(da.cap_rows) : ga.a_rows)) {
+    report_status(w.status, ST_OVERFLOW);
+    if (w.status != nullptr) atomicMax(w.status + 1, c.g_row_start[G]);   // rows that were needed
+    c.overflow = 1;
+    c.abort_flag = 1;
   }
+  __syncthreads();
 
   const uint32_t tmem_base = c.tmem_base;
   const int total_tiles = c.total_sched * TN;
@@ -363,6 +374,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
       uint32_t phase = 0;
       int issued = 0;
       bool ok = !c.abort_flag;
+      // L2 eviction priorities (ga.l2_hints): bit 0 keeps the activation chunk that every N-tile
+      // of the sweep re-reads, bit 1 lets the once-streamed weights leave first.
+      const bool hinted = EPI != B200_EPI_ROUTER && (ga.l2_hints & 3) != 0;
+      const uint64_t pol_a = (ga.l2_hints & 1) ? l2_policy_evict_last() : l2_policy_evict_normal();
+      const uint64_t pol_b = (ga.l2_hints & 2) ? l2_policy_evict_first() : l2_policy_evict_normal();
       for (int idx = sched_id; ok && idx < total_tiles; idx += sched_stride) {
         int g, m, n;
         if (!decode_tile(c, G, TN, gm, idx, cursor, g, m, n)) break;
@@ -410,8 +426,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
             // the pair leader's barrier collects the bytes of both CTAs' loads
             if (cta_rank == 0) mbar_expect_tx(&c.full[stage], STAGE_BYTES * 2);
             const uint32_t lead_bar = map_to_cta(&c.full[stage], 0);
-            tma_load_2d_pair(sa, &tmap_a, lead_bar, kb * BK, row0);
-            tma_load_2d_pair(sa + A_STAGE_BYTES, &tmap_b, lead_bar, kb * BK, brow);
+            if (hinted) {
+              tma_load_2d_pair_hint(sa, &tmap_a, lead_bar, kb * BK, row0, pol_a);
+              tma_load_2d_pair_hint(sa + A_STAGE_BYTES, &tmap_b, lead_bar, kb * BK, brow, pol_b);
+            } else {
+              tma_load_2d_pair(sa, &tmap_a, lead_bar, kb * BK, row0);
+              tma_load_2d_pair(sa + A_STAGE_BYTES, &tmap_b, lead_bar, kb * BK, brow);
+            }
+          } else if (hinted) {
+            mbar_expect_tx(&c.full[stage], static_cast<uint32_t>(STAGE_BYTES));
+            tma_load_2d_hint(sa, &tmap_a, &c.full[stage], kb * BK, row0, pol_a);
+            tma_load_2d_hint(sa + A_STAGE_BYTES, &tmap_b, &c.full[stage], kb * BK, brow, pol_b);
           } else {
             // the router's weight box holds only mma_n rows (the host encodes its map that way)
             const uint32_t tx = (EPI == B200_EPI_ROUTER && ga.mma_n > 0)
@@ -491,7 +516,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
     constexpr int PASSES = OUT_TILE / STG_COLS;
     const int q = warp & 3;                      // TMEM lane quarter this warp may read
     const int row_in_tile = q * 32 + lane;
-    uint8_t* my_stg = staging + row_in_tile * STG_ROW_BYTES;
+    // this warp's 32 x 64 staging box; the 16-byte chunk j of row r sits at chunk j ^ (r & 7)
+    // (the 128-byte swizzle of a TMA store box, and conflict-free for the accesses below)
+    uint8_t* warp_stg = staging + q * STG_WARP_BYTES;
+    uint8_t* my_stg = warp_stg + lane * STG_ROW_BYTES;
+    const uint64_t pol_o = l2_policy_evict_first();
+    bool store_pending = false;   // lane 0: a bulk store may still be reading the staging box
     int cursor = 0, it = 0;
     int pending_arrivals = 0;   // combine epilogue: rows stored for rank `lane`, not yet published
     // accumulators are handed back on the pair leader's barrier
@@ -619,9 +649,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
                                       __uint_as_float(v[2 * i + 1]) * wgt);
             }
           }
+          if (h == 0 && store_pending) {   // the previous pass's bulk store must have read the box
+            bulk_wait_group_read<0>();
+            store_pending = false;
+          }
+          if (h == 0) __syncwarp();
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            *reinterpret_cast<uint4*>(my_stg + h * 64 + i * 16) =
+            *reinterpret_cast<uint4*>(my_stg + (((h * 4 + i) ^ (lane & 7)) << 4)) =
                 make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
           }
         }
@@ -631,9 +666,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
           if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_addr[acc]);
           else mbar_arrive(&c.tmem_empty[acc]);
         }
+        const int box_col0 = n * OUT_TILE + p * STG_COLS;
+        if (EPI != B200_EPI_COMBINE && ga.tma_store && rows_in_tile >= (q + 1) * 32) {
+          // all 32 rows of this warp are rows of the group: one bulk tensor store writes the box
+          // (columns past the output width are clipped by the tensor map)
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0 && box_col0 < ga.n_out) {
+            if (ga.l2_hints & 4) tma_store_2d_hint(&tmap_o, warp_stg, box_col0, row0 + q * 32, pol_o);
+            else tma_store_2d(&tmap_o, warp_stg, box_col0, row0 + q * 32);
+            bulk_commit_group();
+            store_pending = true;
+          }
+          continue;
+        }
         __syncwarp();
-        // coalesced write-out: 8 lanes cover one 128-byte row segment, 4 rows per step
-        const int col0 = n * OUT_TILE + p * STG_COLS + (lane & 7) * 8;
+        // ragged tile or scattered rows: coalesced write-out, 8 lanes cover one 128-byte row
+        // segment, 4 rows per step
+        const int col0 = box_col0 + (lane & 7) * 8;
 #pragma unroll
         for (int rr = 0; rr < 8; ++rr) {
           const int r = rr * 4 + (lane >> 3);
@@ -641,7 +691,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
           const int rvalid = __shfl_sync(0xffffffffu, valid ? 1 : 0, r);
           if (rvalid && col0 < ga.n_out) {
             const uint4 val = *reinterpret_cast<const uint4*>(
-                staging + (q * 32 + r) * STG_ROW_BYTES + (lane & 7) * 16);
+                warp_stg + r * STG_ROW_BYTES + (((lane & 7) ^ (r & 7)) << 4));
             st_16(reinterpret_cast<void*>(dst + static_cast<unsigned long long>(col0) * 2ull), val);
           }
         }
@@ -666,6 +716,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
         }
       }
     }
+    if (store_pending) bulk_wait_group<0>();   // shared memory stays allocated until the stores are done
     if constexpr (EPI == B200_EPI_COMBINE) {
       __syncwarp();
       if (lane < ca.world && pending_arrivals > 0) {
@@ -680,7 +731,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
       const int stid = tid - NUM_THREADS_PLAIN;   // index inside the sender group
       const int swarp = stid >> 5;
       const int ET = da.world * da.e_local;
-      const int total_units = c.total_units;
+      const int total_units = c.overflow ? 0 : c.total_units;   // uniform: written during set-up only
       const int k16 = ga.K / 8;                 // 16-byte chunks per token row
       int bcur = 0;
       // The loop bound is uniform over the sender warps (they meet at a
@@ -732,12 +783,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
         // all sender warps have stored their rows of this unit
         asm volatile("bar.sync 1, %0;" ::"n"(SENDER_WARPS * 32) : "memory");
         if (stid == 0 && !da.drop_signal) {
-          fence_acq_rel_sys();
-          red_add_release_sys(reinterpret_cast<uint32_t*>(da.peer_ready[dst]) +
-                                  c.b_dst_mtile0[bcur] + tile,
-                              static_cast<uint32_t>(p_hi - p_lo));
-          if (da.trace != nullptr && dst == da.rank && c.b_dst_mtile0[bcur] + tile < da.trace_tiles)
-            da.trace[2 + da.trace_tiles + c.b_dst_mtile0[bcur] + tile] = globaltimer_ns();
+          // Only rows that were stored are announced, and only into the counter array's bounds
+          // (rows past the receive capacity were skipped above and reported).
+          const int mt = c.b_dst_mtile0[bcur] + tile;
+          const int stored = min(p_hi, da.cap_rows - drow0) - p_lo;
+          if (mt >= da.cap_mtiles) {
+            report_status(w.status, ST_BAD_INDEX);
+          } else if (stored > 0) {
+            fence_acq_rel_sys();
+            red_add_release_sys(reinterpret_cast<uint32_t*>(da.peer_ready[dst]) + mt,
+                                static_cast<uint32_t>(stored));
+            if (da.trace != nullptr && dst == da.rank && mt < da.trace_tiles)
+              da.trace[2 + da.trace_tiles + mt] = globaltimer_ns();
+          }
         }
       }
     }
@@ -790,12 +848,16 @@ static int make_tmap_bf16(CUtensorMap* tm, const void* base, long long rows, lon
   return r == CUDA_SUCCESS ? 0 : -3;
 }
 
+// Error code of launch_variant when not even one CTA (pair) of the variant can be resident.
+constexpr int ERR_NOT_RESIDENT = -18;
+
 template <int EPI, bool FUSED, int CG>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta1, const CUtensorMap& tb,
-                          const b200_gemm_args& ga,
+                          const CUtensorMap& to, const b200_gemm_args& ga,
                           const b200_dispatch_args& da, const b200_combine_args& ca,
                           const b200_router_args& ra, int ctas, cudaStream_t stream) {
   static bool configured = false;
+  static int resident_clusters = -1;
   auto kern = grouped_gemm_kernel<EPI, FUSED, CG>;
   constexpr int smem = Geo<CG>::SMEM_BYTES;
   if (!configured) {
@@ -816,8 +878,45 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta1, const C
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  // The kernel is persistent and its CTAs wait on one another (sender work is strided over the
+  // whole grid; consumers here and on other ranks poll for it), so every CTA must be resident
+  // at once: the grid is clamped to what this context can hold (asked once per variant).
+  if (resident_clusters < 0) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) {
+      (void)cudaGetLastError();
+      n = 0;
+    }
+    resident_clusters = n;
+  }
+  if (resident_clusters < 1) return ERR_NOT_RESIDENT;
+  if (static_cast<int>(cfg.gridDim.x) > resident_clusters * CG) cfg.gridDim.x = resident_clusters * CG;
   b200_count_launches(1);
-  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, ta1, tb, ga, da, ca, ra));
+  return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, ta1, tb, to, ga, da, ca, ra));
+}
+
+template <int CG>
+static int launch_geometry(int epi, int fused, const CUtensorMap& ta, const CUtensorMap& ta1,
+                           const CUtensorMap& tb, const CUtensorMap& to, const b200_gemm_args& ga,
+                           const b200_dispatch_args& d, const b200_combine_args& c,
+                           const b200_router_args& r, int ctas, cudaStream_t st) {
+  if (!fused) {
+    switch (epi) {
+      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, false, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, false, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, false, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_ROUTER:
+        if constexpr (CG == 1) return launch_variant<B200_EPI_ROUTER, false, 1>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+        break;
+    }
+  } else {
+    switch (epi) {
+      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, true, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, true, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, true, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+    }
+  }
+  return -15;
 }
 
 }  // namespace b200
@@ -828,6 +927,11 @@ extern "C" {
 // buffer (for the fused-dispatch build: this rank's receive buffer and its
 // capacity), `w` is [G*N, K].  Returns 0 or a negative (descriptor) / positive
 // (cudaError_t) error code.  Nothing is allocated.
+//
+// The kernel is persistent and (in the fused builds) its CTAs and the other ranks wait for
+// one another: it needs its CTAs resident together, so it wants the SMs to itself.  The grid
+// is `num_ctas` clamped to what the context can hold at once; CTA pairs fall back to single
+// CTAs where no pair fits.
 int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, int fused,
                       const b200_gemm_args* ga, const b200_dispatch_args* da,
                       const b200_combine_args* ca, const b200_router_args* ra, int num_ctas,
@@ -838,14 +942,15 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
   const int G = fused ? (da ? da->e_local : 0) : ga->num_groups;
   if (G <= 0 || G > B200_MAX_GROUPS) return -11;
   if (fused && (da == nullptr || da->world * da->e_local > B200_MAX_EXPERTS ||
-                da->world > B200_MAX_WORLD))
+                da->world > B200_MAX_WORLD || da->cap_rows > a_rows || da->cap_mtiles < 1))
     return -12;
   if (epi == B200_EPI_COMBINE && ca == nullptr) return -13;
   if (epi == B200_EPI_ROUTER && (ra == nullptr || ra->num_experts > BN || ra->num_experts < 1 ||
                                  ra->topk < 1 || ra->topk > ROUTER_MAX_K || ra->topk > ra->num_experts))
     return -16;
   if (ga->mma_n != 0 && (ga->mma_n % 16 != 0 || ga->mma_n < 16 || ga->mma_n > BN)) return -17;
-  CUtensorMap ta, ta1, tb;
+  if (num_ctas <= 0) return -14;
+  CUtensorMap ta, ta1, tb, to;
   int r = make_tmap_bf16(&ta, a, a_rows, ga->K, BM);
   if (r != 0) return r;
   // second parity copy of the receive buffer (fused build with device-side iteration state)
@@ -854,10 +959,6 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
                        : a;
   r = make_tmap_bf16(&ta1, a1, a_rows, ga->K, BM);
   if (r != 0) return r;
-  int b_box = (ga->cta_pair != 0 && num_ctas >= 2) ? BN / 2 : BN;
-  if (epi == B200_EPI_ROUTER && ga->mma_n > 0) b_box = ga->mma_n;   // few experts: a short weight box
-  r = make_tmap_bf16(&tb, w, static_cast<long long>(G) * ga->N, ga->K, b_box);
-  if (r != 0) return r - 10;
   b200_dispatch_args dz;
   b200_combine_args cz;
   b200_router_args rz;
@@ -868,42 +969,57 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
   const b200_dispatch_args& d = da ? *da : dz;
   const b200_combine_args& c = ca ? *ca : cz;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (num_ctas <= 0) return -14;
-  const bool pair = ga->cta_pair != 0 && num_ctas >= 2;
-  // L2 blocking: a chunk of `group_m` M-tiles of A is swept across all N-tiles and should stay
-  // resident in L2 meanwhile (126 MB L2 shared with the streamed weights and the output); larger
-  // chunks re-read A from HBM once per N-tile, smaller ones re-read the weights more often.
-  // Measured on B200 with K = 14336: chunks of 22-44 MB run 8-10 % faster than 117 MB chunks under
-  // sustained (power-capped) load, while short cool runs prefer the largest chunk by 4-5 %;
-  // about 48 MB per chunk, at most 16 M-tiles, is the compromise.
   b200_gemm_args ga_auto = *ga;
-  if (ga_auto.group_m <= 0) {
-    const long long tile_bytes = static_cast<long long>(pair ? 2 * BM : BM) * ga->K * 2;
-    long long gm = (48ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
-    ga_auto.group_m = static_cast<int>(gm < 1 ? 1 : (gm > 16 ? 16 : gm));
-  }
-  ga = &ga_auto;
-  if (!fused) {
-    switch (epi) {
-      case B200_EPI_STORE: return (pair ? launch_variant<B200_EPI_STORE, false, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_STORE, false, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_SILU_GATE: return (pair ? launch_variant<B200_EPI_SILU_GATE, false, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_SILU_GATE, false, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_COMBINE: return (pair ? launch_variant<B200_EPI_COMBINE, false, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_COMBINE, false, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_ROUTER: return launch_variant<B200_EPI_ROUTER, false, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st);
-    }
+  ga_auto.a_rows = a_rows;
+  // EPI 0/1: boxes of 32 full rows x 64 columns leave through bulk tensor stores when the
+  // output rows are 16-byte aligned; ragged boxes take the per-lane path.
+  to = ta;
+  const bool plain_out = epi == B200_EPI_STORE || epi == B200_EPI_SILU_GATE;
+  if (plain_out && ga->tma_store >= 0 && ga->out != nullptr && ga->ldo >= ga->n_out &&
+      (ga->ldo * 2) % 16 == 0 && (reinterpret_cast<uintptr_t>(ga->out) & 15u) == 0) {
+    EncodeTiledFn enc = get_encode_fn();
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(ga->n_out), static_cast<cuuint64_t>(a_rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ga->ldo) * 2};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(STG_COLS), 32u};
+    cuuint32_t estr[2] = {1, 1};
+    ga_auto.tma_store =
+        (enc != nullptr &&
+         enc(&to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, ga->out, dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+            ? 1
+            : 0;
+    if (!ga_auto.tma_store) to = ta;
   } else {
-    switch (epi) {
-      case B200_EPI_STORE: return (pair ? launch_variant<B200_EPI_STORE, true, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_STORE, true, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_SILU_GATE: return (pair ? launch_variant<B200_EPI_SILU_GATE, true, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_SILU_GATE, true, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
-      case B200_EPI_COMBINE: return (pair ? launch_variant<B200_EPI_COMBINE, true, 2>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st)
-                  : launch_variant<B200_EPI_COMBINE, true, 1>(ta, ta1, tb, *ga, d, c, r2, num_ctas, st));
-    }
+    ga_auto.tma_store = 0;
   }
-  return -15;
+  bool pair = ga->cta_pair != 0 && num_ctas >= 2 && epi != B200_EPI_ROUTER;
+  for (int attempt = 0; attempt < 2; ++attempt) {
+    int b_box = pair ? BN / 2 : BN;
+    if (epi == B200_EPI_ROUTER && ga->mma_n > 0) b_box = ga->mma_n;   // few experts: a short weight box
+    r = make_tmap_bf16(&tb, w, static_cast<long long>(G) * ga->N, ga->K, b_box);
+    if (r != 0) return r - 10;
+    // L2 blocking: a chunk of `group_m` M-tiles of A is swept across all N-tiles and should stay
+    // resident in L2 meanwhile (126 MB L2 shared with the streamed weights and the output); larger
+    // chunks re-read A from HBM once per N-tile, smaller ones re-read the weights more often.
+    // Measured on B200 with K = 14336: chunks of 22-44 MB run 8-10 % faster than 117 MB chunks under
+    // sustained (power-capped) load, while short cool runs prefer the largest chunk by 4-5 %;
+    // about 48 MB per chunk, at most 16 M-tiles, is the compromise.
+    if (ga->group_m <= 0) {
+      const long long tile_bytes = static_cast<long long>(pair ? 2 * BM : BM) * ga->K * 2;
+      long long gm = (48ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
+      ga_auto.group_m = static_cast<int>(gm < 1 ? 1 : (gm > 16 ? 16 : gm));
+    }
+    ga_auto.cta_pair = pair ? 1 : 0;
+    r = pair ? launch_geometry<2>(epi, fused, ta, ta1, tb, to, ga_auto, d, c, r2, num_ctas, st)
+             : launch_geometry<1>(epi, fused, ta, ta1, tb, to, ga_auto, d, c, r2, num_ctas, st);
+    if (r == ERR_NOT_RESIDENT && pair) {   // no pair fits in this context: single-CTA tiles
+      pair = false;
+      continue;
+    }
+    return r;
+  }
+  return r;
 }
 
 int b200_gemm_smem_bytes() { return b200::Geo<1>::SMEM_BYTES; }

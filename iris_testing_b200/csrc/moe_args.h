@@ -33,6 +33,7 @@ typedef struct {
   const uint32_t* counts_flag;    // [world], epoch stamped by each source rank
   uint32_t epoch;                 // 1-based iteration stamp expected in counts_flag
   int cap_rows;                   // receive capacity (rows) of every rank
+  int cap_mtiles;                 // entries of every rank's tile-ready counter array
   int drop_signal;                // testing aid: do not signal tile arrival
   unsigned long long peer_recv[B200_MAX_WORLD];   // bf16 [cap_rows, K]
   unsigned long long peer_meta[B200_MAX_WORLD];   // uint2 [cap_rows]: {src<<24|send position, weight}
@@ -81,6 +82,12 @@ typedef struct {
   int cta_pair;                   // 1: two CTAs per MMA (cta_group::2, 256-row tiles)
   const void* a_base;             // activation buffer (same memory the A tensor map covers); used by
                                   // the router build to prefetch whole rows into L2
+  long long a_rows;               // rows of the activation (and EPI 0/1 output) buffer: the group sizes
+                                  // read on the device may not add up to more (filled by the launcher)
+  int l2_hints;                   // L2 eviction priorities: 1 = keep activations (evict last), 2 = stream
+                                  // weights (evict first), 4 = stream the EPI 0/1 output; 0 = none
+  int tma_store;                  // EPI 0/1: full 32-row boxes leave through bulk tensor stores (set by
+                                  // the launcher when the output is 16-byte aligned; -1 on entry forbids it)
 } b200_gemm_args;
 
 // Router epilogue: the accumulator row holds the logits of one token.

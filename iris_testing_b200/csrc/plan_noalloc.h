@@ -27,8 +27,11 @@
 //  * The call allocates nothing: no cudaMalloc / cudaFree, no allocating
 //    library routine, no PyTorch allocator.
 //  * The first call on each device looks up the array's device address (once
-//    per device, with that device current).  Make that first call outside any
-//    stream capture.
+//    per device, with that device current) and caches it.  Make that first call
+//    outside any stream capture.  Host threads may make it concurrently.  The
+//    cached address belongs to the device's primary context: after a
+//    cudaDeviceReset() the library must be reloaded before this entry point is
+//    used again on that device.
 //  * All calls on one device share the one array.  Its contents after a call
 //    are whatever that call left; nothing in it has to be zero on entry,
 //    because each call writes every element before reading it.  Two calls

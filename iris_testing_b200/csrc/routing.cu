@@ -11,6 +11,8 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "moe_args.h"
 #include "sm100_ptx.cuh"
 #include "topk.cuh"
@@ -292,7 +294,9 @@ namespace b200 {
 static __device__ __align__(256) int g_plan_scratch[B200_PLAN_NOALLOC_MAX];
 
 constexpr int kMaxDevices = 64;
-static int* g_plan_scratch_addr[kMaxDevices] = {nullptr};
+// Device address of the array per device.  Atomic so that two host threads making the first
+// call together is harmless (both resolve the same address; nothing is allocated either way).
+static std::atomic<int*> g_plan_scratch_addr[kMaxDevices];
 }  // namespace b200
 
 extern "C" {
@@ -310,14 +314,15 @@ int b200_plan_noalloc(const int* topk_idx, int n_flat, int num_experts, int* cou
   if (e != cudaSuccess) return static_cast<int>(e);
   if (dev < 0 || dev >= b200::kMaxDevices) return B200_PLAN_NOALLOC_NO_DEVICE;
   // once per device, with that device current: resolve the array's device address
-  if (b200::g_plan_scratch_addr[dev] == nullptr) {
+  int* scratch = b200::g_plan_scratch_addr[dev].load(std::memory_order_relaxed);
+  if (scratch == nullptr) {
     int* p = nullptr;
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), b200::g_plan_scratch);
     if (e != cudaSuccess) return static_cast<int>(e);
     if (p == nullptr) return B200_PLAN_NOALLOC_NO_DEVICE;
-    b200::g_plan_scratch_addr[dev] = p;
+    b200::g_plan_scratch_addr[dev].store(p, std::memory_order_relaxed);
+    scratch = p;
   }
-  int* scratch = b200::g_plan_scratch_addr[dev];
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   b200::plan_rank_kernel<<<num_experts, 1024, 0, st>>>(topk_idx, n_flat, num_experts, scratch, counts);
   b200_count_launches(1);

@@ -285,6 +285,7 @@ class MoELayer(nn.Module):
         da.counts_all = self.counts_all[0].data_ptr()
         da.counts_flag = self.counts_flag[0].data_ptr()
         da.cap_rows = self.cap_rows
+        da.cap_mtiles = self.cap_mtiles
         da.drop_signal = int(self.drop_signal)
         da.peer_recv = heap.peer_ptrs(self.recv[0])
         da.peer_meta = heap.peer_ptrs(self.meta[0])

@@ -14,7 +14,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _native as nv
-from ._common import declare, ptr, require, stream_ptr
+from ._common import declare, default_status, ptr, require, stream_ptr
 from .dispatch import _heap_of, tile_rows
 
 
@@ -69,7 +69,7 @@ def weighted_gather(ret_buf: torch.Tensor, plan, topk_idx: torch.Tensor, topk_w:
                   C.c_void_p, C.c_ulonglong, C.c_void_p])
     y = torch.empty((T, H), dtype=ret_buf.dtype, device=ret_buf.device)
     if status is None:
-        status = torch.zeros(4, dtype=torch.int32, device=ret_buf.device)
+        status = default_status(ret_buf.device)
     if ret_sync is None:   # nothing to wait for: an all-zero expectation is met by any counter
         ret_sync = torch.full((world,), 2 ** 30, dtype=torch.int32, device=ret_buf.device)
     rc = fn(ptr(ret_buf), ptr(plan.dst_slot), ptr(topk_idx), ptr(plan.bucket_start), ptr(topk_w),

@@ -15,7 +15,7 @@ import torch
 
 from .. import _native as nv
 from . import cpu_ref
-from ._common import contiguous_bf16, ptr, require, stream_ptr, use_native
+from ._common import contiguous_bf16, default_status, ptr, require, stream_ptr, use_native
 
 _SM_COUNT = {}
 
@@ -80,7 +80,7 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     if M == 0:
         return out
     if status is None:
-        status = torch.zeros(4, dtype=torch.int32, device=a.device)
+        status = default_status(a.device)
     ga = nv.GemmArgs()
     ga.num_groups, ga.N, ga.K, ga.n_out, ga.group_m = G, N, K, n_out, group_m
     ga.group_rows = group_rows.data_ptr()

@@ -12,7 +12,7 @@ from typing import Optional
 import torch
 
 from . import cpu_ref
-from ._common import contiguous_bf16, declare, ptr, require, stream_ptr, use_native
+from ._common import contiguous_bf16, declare, default_status, ptr, require, stream_ptr, use_native
 
 MAX_TOPK = 8
 
@@ -85,7 +85,7 @@ def _router_tensor_core(x, wr_kmajor, bias, topk, renormalize, idx, w, status=No
     T, D = x.shape
     E = wr_kmajor.shape[0]
     if status is None:
-        status = torch.zeros(4, dtype=torch.int32, device=x.device)
+        status = default_status(x.device)
     ga = nv.GemmArgs()
     ga.num_groups, ga.N, ga.K, ga.n_out, ga.group_m = 1, E, D, E, 16
     ga.group_rows = None

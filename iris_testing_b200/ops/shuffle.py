@@ -16,14 +16,14 @@ import torch
 
 from .. import _native as nv
 from . import cpu_ref
-from ._common import declare, ptr, require, stream_ptr
+from ._common import declare, default_status, ptr, require, stream_ptr
 from .dispatch import tile_rows
 
 
 def _fn():
     return declare("b200_shuffle", [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                     C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
-                                    C.c_void_p, C.c_void_p, C.c_ulonglong, C.c_void_p])
+                                    C.c_void_p, C.c_int, C.c_void_p, C.c_ulonglong, C.c_void_p])
 
 
 def shuffle(dispatched_tokens: torch.Tensor, pca: torch.Tensor, token_sync: Optional[torch.Tensor] = None,
@@ -35,6 +35,9 @@ def shuffle(dispatched_tokens: torch.Tensor, pca: torch.Tensor, token_sync: Opti
     When ``token_sync`` and ``counts_ready`` are given the kernel first waits (bounded) for
     the dispatch to land.  On CUDA ``packed`` has ``max_rows`` rows (default: every cell
     full) so that no host synchronisation is needed; only the first ``sum(rows)`` are valid.
+    More valid rows than ``max_rows`` are not copied: the kernel records an overflow (with the
+    number of rows needed) in ``status`` -- the device's default status word when none is given,
+    see :func:`iris_testing_b200.ops.check_default_status`.
     """
     e_local, world, cap, H = dispatched_tokens.shape
     if not dispatched_tokens.is_cuda:
@@ -46,9 +49,9 @@ def shuffle(dispatched_tokens: torch.Tensor, pca: torch.Tensor, token_sync: Opti
     group_rows = torch.empty((e_local,), dtype=torch.int32, device=pca.device)
     wait = int(token_sync is not None and counts_ready is not None)
     if status is None:
-        status = torch.zeros(4, dtype=torch.int32, device=pca.device)
+        status = default_status(pca.device)
     rc = _fn()(ptr(dispatched_tokens), ptr(packed), ptr(pca), ptr(counts_ready), ptr(token_sync),
-               world, e_local, cap, H, tile_rows(), wait, 0, ptr(group_rows), ptr(status),
+               world, e_local, cap, H, tile_rows(), wait, 0, ptr(group_rows), rows, ptr(status),
                int(wait_budget_ms * 1e6), stream_ptr(pca))
     nv.check(rc, "shuffle launch")
     return packed, group_rows
@@ -67,9 +70,8 @@ def unshuffle(packed: torch.Tensor, pca: torch.Tensor, capacity: int,
         return cpu_ref.unshuffle_ref(packed, pca, capacity)
     if out is None:
         out = torch.zeros((e_local, world, capacity, H), dtype=packed.dtype, device=packed.device)
-    status = torch.zeros(4, dtype=torch.int32, device=pca.device)
     rc = _fn()(ptr(out), ptr(packed), ptr(pca), None, None, world, e_local, capacity, H, tile_rows(),
-               0, 1, None, ptr(status), 0, stream_ptr(pca))
+               0, 1, None, packed.shape[0], ptr(default_status(pca.device)), 0, stream_ptr(pca))
     nv.check(rc, "unshuffle launch")
     return out
 

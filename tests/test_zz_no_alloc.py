@@ -57,6 +57,16 @@ def test_plan_noalloc_matches_regular_entry_point_twice():
         torch.cuda.synchronize()
         assert torch.equal(counts, r_counts) and torch.equal(start, r_start)
         assert torch.equal(order, r_order) and torch.equal(slot, r_slot)
+    # dst_slot is optional: without it the other outputs are unchanged
+    order2 = torch.empty(n, **i32)
+    assert fn(idx.data_ptr(), n, E, counts.data_ptr(), start.data_ptr(), order2.data_ptr(), None, stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(order2, r_order) and torch.equal(counts, r_counts)
+    # no routed copies at all: zero counts, an all-zero scan, nothing else touched
+    assert fn(idx.data_ptr(), 0, E, counts.data_ptr(), start.data_ptr(), order2.data_ptr(), None, stream) == 0
+    torch.cuda.synchronize()
+    assert int(counts.abs().sum()) == 0 and int(start.abs().sum()) == 0
+    assert torch.equal(order2, r_order)
     # beyond the stated maximum: a clear error and nothing launched
     assert fn(idx.data_ptr(), limit + 1, 8, counts.data_ptr(), start.data_ptr(), order.data_ptr(),
               slot.data_ptr(), stream) == -20
