@@ -20,6 +20,8 @@ EPI_SILU_GATE = 1
 EPI_COMBINE = 2
 EPI_ROUTER = 3
 
+ST_OVERFLOW = 10      # status code: routed rows exceed a buffer's capacity
+
 STATUS_NAMES = {
     0: "ok",
     1: "timeout: TMA data never arrived in shared memory",

@@ -23,7 +23,8 @@ class MoEConfig:
     gated: bool = True              # SiLU-gated MLP (W1, W3, W2); False: a single Linear D -> ffn_dim
     renormalize: bool = False       # renormalise the top-k softmax weights to sum to 1
     dtype: torch.dtype = torch.bfloat16
-    capacity_factor: Optional[float] = None   # None: worst case (every token of every rank)
+    capacity_factor: Optional[float] = 1.25   # receive capacity over the balanced load; None: worst case
+                                              # (every routed copy of every rank), world_size x the memory
     wait_budget_ms: float = 2000.0  # budget of every bounded device-side wait
     cta_pair: Optional[bool] = None  # two CTAs per MMA (cta_group::2); None: when experts average >= 256 rows
 

@@ -1,5 +1,5 @@
-// Symmetric heap runtime: one device allocation per rank, exported with CUDA
-// IPC and mapped by every other rank of the node, so that kernels can address
+// Symmetric heap runtime, fallback back-end (the primary one is vmm_heap.cu): one device
+// allocation per rank, exported with CUDA IPC and mapped by every other rank of the node, so that kernels can address
 // any rank's copy of a buffer as base[rank] + offset and reach it with plain
 // loads/stores over NVLink.  Plays the role the external `iris` library plays
 // for the reference project (benchmark.py:38-42, utils.py:48-80: a fixed-size
@@ -66,6 +66,12 @@ int b200_heap_close(int device, void* mapped) {
 
 int b200_memset_async(void* ptr, int value, unsigned long long bytes, void* stream) {
   return static_cast<int>(cudaMemsetAsync(ptr, value, bytes, static_cast<cudaStream_t>(stream)));
+}
+
+// One device-to-device copy; either address may be a peer's mapped memory.
+int b200_memcpy_async(void* dst, const void* src, unsigned long long bytes, void* stream) {
+  return static_cast<int>(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice,
+                                          static_cast<cudaStream_t>(stream)));
 }
 
 void b200_count_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }

@@ -42,6 +42,7 @@ from ..ops.router import router_topk
 from ..utils import gen
 
 _NVTX = os.getenv("B200MOE_NVTX", "0") == "1"   # NVTX range around every forward
+_CANARY = 0x5A5A5A5A
 BM = 128          # rows per GEMM tile
 BN = 256          # weight rows per GEMM tile
 
@@ -70,12 +71,20 @@ def heap_bytes_needed(cfg: MoEConfig, max_tokens: int, cap_rows: Optional[int] =
 
 
 def default_cap_rows(cfg: MoEConfig, max_tokens: int) -> int:
+    """Receive capacity (rows) of every rank.
+
+    Balanced routing gives a rank ``max_tokens * topk`` rows; ``capacity_factor`` (default
+    1.25) scales that, plus one tile of slack per local expert.  ``capacity_factor=None``
+    sizes for the worst case (every routed copy of every rank lands on one rank), which can
+    never overflow but costs ``world_size`` times the memory.  A step that needs more rows
+    than the capacity reports an overflow with the number needed;
+    :meth:`MoELayer.forward_checked` grows the buffers and repeats the step."""
     worst = cfg.world_size * max_tokens * cfg.topk
     if cfg.capacity_factor is None:
         rows = worst
     else:
         rows = min(worst, int(cfg.capacity_factor * max_tokens * cfg.topk) + cfg.e_local * BM)
-    return (rows + BM - 1) // BM * BM
+    return (max(rows, BM) + BM - 1) // BM * BM
 
 
 class MoELayer(nn.Module):
@@ -94,7 +103,8 @@ class MoELayer(nn.Module):
 
     def __init__(self, cfg: MoEConfig, max_tokens: int, heap=None, device=None, seed: int = 0,
                  rank: Optional[int] = None, router_std: Optional[float] = None,
-                 cap_rows: Optional[int] = None) -> None:
+                 cap_rows: Optional[int] = None, num_ctas: Optional[int] = None,
+                 debug_canaries: bool = False) -> None:
         super().__init__()
         self.cfg = cfg
         self.max_tokens = int(max_tokens)
@@ -122,6 +132,9 @@ class MoELayer(nn.Module):
         self._iteration = 0
         self._engine_ready = False
         self._cap_rows = cap_rows
+        self._num_ctas = num_ctas       # persistent grid of the GEMM kernels (default: one CTA per SM)
+        self._debug_canaries = bool(debug_canaries)
+        self._canaries = []
         self.drop_signal = False        # fault-injection aid for the timeout test
         self.profile = False            # record CUDA events between the phases of forward()
         self.phase_events = []
@@ -167,22 +180,19 @@ class MoELayer(nn.Module):
             raise ValueError("max_tokens * topk must stay below 2^24")
         dev = heap.device
         cap = self._cap_rows if self._cap_rows is not None else default_cap_rows(cfg, T)
-        self.cap_rows = cap
-        self.cap_mtiles = cap // BM + EL + 1
         u32 = torch.int32
-        # symmetric state (identical offsets on every rank)
-        self.recv = heap.empty((2, cap, D), cfg.dtype)
-        self.meta = heap.zeros((2, cap, 2), u32)
-        self.ready = heap.zeros((2, self.cap_mtiles), u32)
+        # symmetric state (identical offsets on every rank).  Fixed-size part first, so that the
+        # capacity-dependent buffers sit at the end of the heap and can be re-made larger.
+        self._guard()
         self.counts_all = heap.zeros((2, W, ET), u32)
         self.counts_flag = heap.zeros((2, W), u32)
         self.iter_done = heap.zeros((W,), u32)
-        self.out_slots = heap.empty((T * k, cfg.out_dim), cfg.dtype)
         self.arrived = heap.zeros((1,), u32)
+        self._guard()
+        self.out_slots = heap.empty((T * k, cfg.out_dim), cfg.dtype)
+        self._guard()
         # local state
         i32 = dict(dtype=torch.int32, device=dev)
-        self.hidden = (torch.empty((cap, cfg.ffn_dim), dtype=cfg.dtype, device=dev)
-                       if cfg.gated else None)
         self.group_rows = torch.zeros(EL, **i32)
         self.ticket = torch.zeros(1, **i32)
         # iteration number, kept on the device: kernels read it and the last kernel of a forward
@@ -195,17 +205,125 @@ class MoELayer(nn.Module):
             "b200_slot_reduce",
             [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_int, C.c_int, C.c_int, C.c_void_p,
              C.POINTER(RetireArgs), C.c_void_p, C.c_ulonglong, C.c_void_p])
-        self._ctas = sm_count(dev)
+        self._ctas = int(self._num_ctas) if self._num_ctas else sm_count(dev)
         pair = cfg.cta_pair
         if pair is None:      # 256-row tiles pay off once an expert sees a few of them
             pair = (T * k * W) // max(ET, 1) >= 256
         self._cta_pair = int(bool(pair))
         self._budget_ns = int(cfg.wait_budget_ms * 1e6)
+        self.recv = self.meta = self.ready = self.hidden = None
+        self._alloc_capacity(cap)
         # every rank's buffers exist and are zeroed before anyone dispatches
         torch.cuda.synchronize(dev)
         if W > 1:
             dist.barrier(group=heap.group)
         self._engine_ready = True
+
+    def _guard(self) -> None:
+        """Debug aid: a guard block of known words between two symmetric buffers."""
+        if self._debug_canaries:
+            g = self.heap.empty((256,), torch.int32)
+            g.fill_(_CANARY)
+            self._canaries.append(g)
+
+    def check_canaries(self) -> None:
+        """Raise if any guard block around the symmetric buffers was written to (needs
+        ``debug_canaries=True``).  Synchronises."""
+        for i, g in enumerate(self._canaries):
+            bad = int((g != _CANARY).sum().item())
+            if bad:
+                raise nv.NativeError(f"rank {self.rank}: guard block {i} of the symmetric buffers was "
+                                     f"overwritten ({bad} of {g.numel()} words)")
+
+    def _alloc_capacity(self, cap: int) -> None:
+        """(Re)make the buffers whose size follows the receive capacity."""
+        cfg, heap = self.cfg, self.heap
+        D, EL = cfg.hidden_dim, cfg.e_local
+        guards = self._canaries[self._fixed_guards:] if self.recv is not None else []
+        for t in [*reversed(guards), self.ready, self.meta, self.recv]:   # reverse order: the heap's tail shrinks
+            if t is not None:
+                heap.free(t)
+        if self.recv is not None:
+            del self._canaries[self._fixed_guards:]
+        else:
+            self._fixed_guards = len(self._canaries)
+        self.cap_rows = int(cap)
+        self.cap_mtiles = self.cap_rows // BM + EL + 1
+        self.recv = heap.empty((2, self.cap_rows, D), cfg.dtype)
+        self._guard()
+        self.meta = heap.zeros((2, self.cap_rows, 2), torch.int32)
+        self._guard()
+        self.ready = heap.zeros((2, self.cap_mtiles), torch.int32)
+        self._guard()
+        self.hidden = (torch.empty((self.cap_rows, cfg.ffn_dim), dtype=cfg.dtype, device=heap.device)
+                       if cfg.gated else None)
+        self._trace = None
+        self._graph = None
+
+    def memory_bytes(self) -> dict:
+        """Bytes this layer holds per rank: symmetric (peer-visible) and local buffers, weights apart."""
+        sym = sum(t.numel() * t.element_size() for t in
+                  (self.recv, self.meta, self.ready, self.counts_all, self.counts_flag, self.iter_done,
+                   self.out_slots, self.arrived))
+        local = (self.hidden.numel() * 2 if self.hidden is not None else 0)
+        local += sum(t.numel() * 4 for t in (self._plan.send_order, self._plan.dst_slot, self._plan.rank_in_bucket))
+        return dict(symmetric=int(sym), local=int(local), capacity_rows=self.cap_rows,
+                    balanced_rows=self.max_tokens * self.cfg.topk)
+
+    # ------------------------------------------------------------ capacity
+    def reset_state(self) -> None:
+        """Collective: bring the cross-rank counters back to their between-steps state after a
+        step that failed on some rank (overflow, timeout).  Synchronises every rank."""
+        W = self.cfg.world_size
+        torch.cuda.synchronize(self.heap.device)
+        if W > 1:
+            dist.barrier(group=self.heap.group)          # nobody is still writing into a peer
+        self.arrived.zero_()
+        self.ready.zero_()
+        self.ticket.zero_()
+        self.heap.status.zero_()
+        torch.cuda.synchronize(self.heap.device)
+        if W > 1:
+            dist.barrier(group=self.heap.group)
+
+    def resize(self, cap_rows: int) -> None:
+        """Collective: re-make the receive buffers for ``cap_rows`` rows per rank (rounded up to
+        a tile).  Every rank must call it with the same value, between steps."""
+        cap = (int(cap_rows) + BM - 1) // BM * BM
+        self.reset_state()
+        self._alloc_capacity(cap)
+        torch.cuda.synchronize(self.heap.device)
+        if self.cfg.world_size > 1:
+            dist.barrier(group=self.heap.group)
+
+    def forward_checked(self, x: torch.Tensor, max_retries: int = 3, growth: float = 1.1) -> torch.Tensor:
+        """``forward`` followed by a status check on every rank (a host synchronisation).
+
+        When some rank's routed rows exceeded the receive capacity, every rank re-makes its
+        buffers for the largest number of rows any rank needed (times ``growth``) and the step
+        is repeated -- what the reference's benchmark can only skip (benchmark.py:133-142).
+        Other failures raise on every rank.  Use it for the first steps of a run (to settle
+        the capacity) or throughout where a host synchronisation per step is acceptable."""
+        W = self.cfg.world_size
+        for attempt in range(max_retries + 1):
+            y = self.forward(x)
+            torch.cuda.synchronize(self.heap.device)
+            st = self.heap.status[:2].clone()
+            code, needed = int(st[0].item()), int(st[1].item())
+            info = torch.tensor([1 if code == nv.ST_OVERFLOW else 0, needed,
+                                 1 if code not in (0, nv.ST_OVERFLOW) else 0, code],
+                                dtype=torch.int64, device=self.heap.device)
+            if W > 1:
+                dist.all_reduce(info, op=dist.ReduceOp.MAX, group=self.heap.group)
+            overflow, needed_max, other, worst = (int(v) for v in info.tolist())
+            if not overflow and not other:
+                return y
+            if not overflow or attempt == max_retries:
+                self.reset_state()
+                raise nv.NativeError(f"rank {self.rank}: step failed with device status {worst}: "
+                                     f"{nv.status_message(worst)} (this rank: {code})")
+            self.resize(max(int(needed_max * growth), self.cap_rows + BM))
+        raise AssertionError("unreachable")
 
     @property
     def launches_per_forward(self) -> int:

@@ -21,20 +21,20 @@ import torch.distributed as dist
 from .. import _native as nv
 from ._common import declare, ptr, require, stream_ptr
 
-_HEAPS = {}   # data_ptr of a heap_bases tensor -> SymmetricHeap
-
-
 def register_heap(heap) -> None:
-    _HEAPS[heap.get_heap_bases().data_ptr()] = heap
+    """Kept for callers of earlier versions: the heap-bases table now carries a weak reference
+    to its heap, so nothing needs registering and nothing outlives the heap."""
+    heap.get_heap_bases()
 
 
 def _heap_of(heap_bases):
     if hasattr(heap_bases, "peer_ptrs"):
         return heap_bases
-    h = _HEAPS.get(heap_bases.data_ptr()) if isinstance(heap_bases, torch.Tensor) else None
-    if h is None:
-        raise ValueError("heap_bases must come from SymmetricHeap.get_heap_bases() "
-                         "(or be the SymmetricHeap itself)")
+    ref = getattr(heap_bases, "_b200_heap", None)
+    h = ref() if ref is not None else None
+    if h is None or h.closed:
+        raise ValueError("heap_bases must be the tensor returned by SymmetricHeap.get_heap_bases() "
+                         "of a live heap (or the SymmetricHeap itself)")
     return h
 
 

@@ -181,13 +181,15 @@ def test_interleave_gate_up_layout():
 
 def test_capacity_and_heap_sizing():
     from iris_testing_b200.models import default_cap_rows, heap_bytes_needed
-    cfg = preset("mixtral-8x7b", world_size=8)
+    import dataclasses
+    tight = preset("mixtral-8x7b", world_size=8)                 # default: 1.25 x the balanced load
+    assert tight.capacity_factor == 1.25
+    cfg = dataclasses.replace(tight, capacity_factor=None)
     worst = default_cap_rows(cfg, 16384)
     assert worst == 8 * 16384 * 2 and worst % 128 == 0          # every token of every rank
-    import dataclasses
-    tight = dataclasses.replace(cfg, capacity_factor=1.25)
     assert default_cap_rows(tight, 16384) < worst
-    assert default_cap_rows(tight, 16384) >= int(1.25 * 16384 * 2)
+    assert int(1.25 * 16384 * 2) <= default_cap_rows(tight, 16384) <= int(1.26 * 16384 * 2)
+    assert default_cap_rows(preset("mixtral-8x7b", world_size=1), 16384) == 16384 * 2   # one rank: worst = balanced
     need = heap_bytes_needed(cfg, 16384)
     assert need > 2 * worst * 4096 * 2                           # two parity copies of the receive buffer
     assert heap_bytes_needed(cfg, 16384, cap_rows=1024) < need
