@@ -1,30 +1,34 @@
 #!/usr/bin/env python
-"""Headline benchmark: latency of one expert-parallel MoE layer (dispatch all-to-all +
-expert GEMMs + combine), Mixtral-8x7B shape, bf16, device-timed, max over ranks.
+"""Two-arm benchmark: this library against the unmodified reference, same loops, same config.
 
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
-    python bench.py --impl reference ...      # the unmodified reference's NCCL path
+    python bench.py --impl reference ...      # the reference's NCCL path (baseline/_ref)
 
-Config (weak scaling: every rank holds its own B*S tokens): D=4096, F=14336, E=8
-(8/N experts per GPU), top-2, SiLU-gated MLP, B=4, S=4096, x ~ N(0,1), router ~
-N(0, 1/D), expert weights ~ N(0, 0.02); seeded synthetic data, random-init weights.
+Default (the headline): latency of one expert-parallel MoE layer -- dispatch all-to-all, expert
+GEMMs, combine -- Mixtral-8x7B shape (D=4096, F=14336, E=8, top-2, SiLU-gated), B=4, S=4096
+tokens per rank (weak scaling), bf16, x ~ N(0,1), router ~ N(0, 1/D), expert weights ~
+N(0, 0.02); seeded synthetic data, random-init weights.  Other configurations:
 
-Rank 0 prints ONE JSON line.  ``value`` is microseconds per layer forward (lower is
-better); ``e2e`` is the same metric through ``MoELayer.forward`` including, every
-step, the host->device copy of that step's tokens from pinned memory and a
-device->host read of the step's result.
+    --model fine-grained [--experts E --topk k]     D=2048, F=1408, B=8, S=2048
+    --model large --zipf 1.2                        D=6144, F=16384, B=8, S=4096, skewed routing
+    --mode a2a [--combine] [--batch B --seq S]      padded all-to-all alone, D=4096, 8 experts/GPU
+
+Rank 0 prints ONE JSON line.  ``value`` is microseconds per step (device-timed with CUDA events,
+max over ranks; lower is better); ``e2e`` is the same step through the public API including,
+every step, the host->device copy of that step's tokens from pinned memory and a device->host
+read of the step's result.  Both arms run the same timing and staging loops
+(``iris_testing_b200/bench_harness.py``) and print the same ``config``.  After the timed regions
+the library arm checks one step against an oracle (``check``) and exits non-zero if it fails.
 """
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
-import statistics
-import subprocess
 import sys
-import tempfile
 import time
 from pathlib import Path
 
@@ -34,249 +38,87 @@ import torch.distributed as dist
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
+from iris_testing_b200.bench_harness import (MODEL_DEFAULTS, ClockSampler, describe_config,  # noqa: E402
+                                             device_timed, e2e_loop, fence, make_config, max_over_ranks)
+
 METRIC = "moe_a2a_gemm_layer_us_max_over_ranks"
+METRIC_A2A = "padded_a2a_us_max_over_ranks"
 
 
-# --------------------------------------------------------------------------- clocks
-class ClockSampler:
-    """Samples nvidia-smi clocks / throttle reasons while the timed region runs."""
-
-    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int) -> None:
-        self.gpu_index = gpu_index
-        self.proc = None
-        self.path = None
-
-    def mark_begin(self) -> None:
-        self.t_begin = time.time()
-
-    def mark_end(self) -> None:
-        self.t_end = time.time()
-
-    def start(self) -> None:
-        self.t_begin, self.t_end = 0.0, float("inf")
-        try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "50", "-i", str(self.gpu_index)],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
-            return
-        # nvidia-smi needs a moment to enumerate the GPUs: wait for its first sample
-        t0 = time.time()
-        while time.time() - t0 < 10.0:
-            try:
-                if os.path.getsize(self.path) > 0:
-                    break
-            except OSError:
-                pass
-            time.sleep(0.05)
-
-    def stop(self) -> dict:
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        if self.proc is None:
-            return out
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, power = [], [], []
-        reasons = set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        try:
-            for line in open(self.path):
-                parts = [p.strip() for p in line.split(",")]
-                if len(parts) < 9:
-                    continue
-                try:   # keep only samples taken inside the timed region
-                    import datetime
-                    ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
-                    if ts < self.t_begin - 0.05 or ts > self.t_end + 0.05:
-                        continue
-                except ValueError:
-                    pass
-                try:
-                    sm.append(float(parts[1])); mx.append(float(parts[2])); power.append(float(parts[3]))
-                except ValueError:
-                    continue
-                for name, val in zip(names, parts[5:9]):
-                    if val.lower().startswith("active"):
-                        reasons.add(name)
-            os.unlink(self.path)
-        except Exception:
-            pass
-        if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons),
-                       samples=len(sm), power_w_max=max(power))
-        return out
-
-
-# --------------------------------------------------------------------------- helpers
 def init_dist(n_gpus: int):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != n_gpus:
-        if n_gpus == 1 and world == 1:
-            pass
-        else:
-            raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+    if world != n_gpus and not (n_gpus == 1 and world == 1):
+        raise SystemExit(f"--gpus {n_gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    return rank, world, local, dev
+    return rank, world, local, torch.device("cuda", local)
 
 
-def max_over_ranks(value: float, dev, world: int) -> float:
-    if world == 1:
-        return value
-    t = torch.tensor([value], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
-def fence(world: int) -> None:
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-
-
-def emit(args, rank, world, us, e2e, launches, clocks, extra_cfg, impl):
+def emit(args, cfg, rank, world, us, e2e, launches, clocks, impl, timed, memory, check, extra=None):
     if rank != 0:
         return
     tokens_total = args.batch * args.seq * world
     line = {
-        "metric": METRIC, "value": round(us, 2), "unit": "us", "n_gpus": world,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(us / 1000.0, 5),
+        "metric": METRIC if args.mode == "layer" else METRIC_A2A, "value": round(us, 2), "unit": "us",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(us / 1000.0, 5),
         "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (seeded N(0,1) tokens, random-init weights)", "impl": impl,
         "tokens_per_s": round(tokens_total / (us * 1e-6), 1),
-        "config": dict(model="mixtral-8x7b MoE layer (D=4096, F=14336, E=8, top-2, SiLU-gated)",
-                       global_batch=args.batch * world, seq_len=args.seq,
-                       tokens_per_rank=args.batch * args.seq, parallelism=f"ep{world}",
-                       l2="inputs alternate between two 134 MB token buffers and expert weights "
-                          "are >= 352 MB per rank: working set exceeds the 126 MB L2",
-                       **extra_cfg),
+        "config": describe_config(args, cfg, world),
         "clocks": clocks, "gpu_launches": launches, "e2e": e2e,
+        "time_x_sm_mhz": (round(us * clocks["sm_mhz"], 0) if clocks.get("sm_mhz") else None),
+        "timed": timed, "memory": memory, "check": check,
     }
+    if extra:
+        line.update(extra)
     print(json.dumps(line), flush=True)
 
 
-# --------------------------------------------------------------------------- our arm
-def run_ours(args) -> None:
-    from iris_testing_b200.config import preset
-    from iris_testing_b200.models.moe_layer import MoELayer, heap_bytes_needed
-    from iris_testing_b200.parallel.symm import SymmetricHeap
-    from iris_testing_b200.utils import gen
+def run_arm(args, arm, cfg, rank, world, local, dev, impl, count_fn=None) -> int:
+    sampler = ClockSampler(local)
+    sampler.start()
+    arm.settle()
+    for i in range(args.warmup):
+        arm.run(arm.inputs[i & 1], i)
+    fence(world)
+    arm.check_status()
+    before = count_fn() if count_fn else 0
+    us = device_timed(arm, args.steps, world, sampler)
+    launches = int(count_fn() - before) if count_fn else 0
+    clocks = sampler.stop()
+    arm.check_status()
+    us = max_over_ranks(us, dev, world)
+    e2e_loop(arm, max(2, min(args.warmup, 3)), world, dev)
+    e2e_us = max_over_ranks(e2e_loop(arm, args.steps, world, dev), dev, world)
+    arm.check_status()
+    e2e = {"value": round(e2e_us, 2), "unit": "us", "h2d_bytes_per_step": arm.h2d_bytes,
+           "d2h_bytes_per_step": 4, "api": arm.api,
+           "loop": "pinned H2D on a copy stream one step ahead, result scalar read one step late (both arms)"}
+    check = arm.check(args.check_tokens) if not args.no_check else None
+    if count_fn and launches != arm.launches_expected(args.steps):      # counted vs expected: report only
+        print(f"note: {launches} launches counted, {arm.launches_expected(args.steps)} expected",
+              file=sys.stderr, flush=True)
+    emit(args, cfg, rank, world, us, e2e, launches, clocks, impl, arm.timed, arm.memory(), check,
+         extra=getattr(arm, "extra", None))
+    return 0 if (check is None or check.get("ok", True)) else 3
 
+
+def run_ours(args) -> int:
+    from iris_testing_b200 import _native
+    from iris_testing_b200.bench_harness import A2AArm, LayerArm
     rank, world, local, dev = init_dist(args.gpus)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    cfg = preset(args.model, world_size=world)
-    T = args.batch * args.seq
-    heap = SymmetricHeap(heap_bytes_needed(cfg, T) + (64 << 20))
-    layer = MoELayer(cfg, max_tokens=T, heap=heap, seed=args.seed, router_std=None)
-    xs = [gen.gen_local_tokens(args.batch, args.seq, cfg.hidden_dim, torch.bfloat16, dev,
-                               args.seed + 1000 * i, rank, "normal") for i in range(2)]
-
-    sampler = ClockSampler(local)
-    sampler.start()
-    for i in range(args.warmup):
-        layer(xs[i & 1])
-    fence(world)
-    layer.check_status()
-
-    # ---- device-timed region
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    fence(world)
-    import ctypes
-    from iris_testing_b200 import _native
+    cfg = make_config(args, world)
+    arm = (LayerArm if args.mode == "layer" else A2AArm)(args, rank, world, dev)
     count_fn = _native.lib().b200_launch_count      # incremented by every native launcher
     count_fn.restype = ctypes.c_longlong
-    launches_before = count_fn()
-    sampler.mark_begin()
-    e0.record()
-    for i in range(args.steps):
-        y = layer(xs[i & 1])
-    e1.record()
-    fence(world)
-    sampler.mark_end()
-    launches = int(count_fn() - launches_before)
-    us = e0.elapsed_time(e1) * 1000.0 / args.steps
-    clocks = sampler.stop()
-    layer.check_status()
-    us = max_over_ranks(us, dev, world)
-
-    # ---- end to end through the public API: pinned H2D of the tokens + D2H of a result scalar
-    hosts = [x.cpu().pin_memory() for x in xs]
-    bufs = [torch.empty_like(xs[0]) for _ in range(2)]
-    copy_stream = torch.cuda.Stream(dev)
-    main = torch.cuda.current_stream(dev)
-    ready = [torch.cuda.Event() for _ in range(2)]
-    freed = [torch.cuda.Event() for _ in range(2)]
-
-    def stage(i: int) -> None:      # H2D of step i's tokens on the copy stream
-        b = i & 1
-        with torch.cuda.stream(copy_stream):
-            copy_stream.wait_event(freed[b])
-            bufs[b].copy_(hosts[b], non_blocking=True)
-            ready[b].record(copy_stream)
-
-    result_host = torch.zeros(2, dtype=torch.float32).pin_memory()
-    result_ready = [torch.cuda.Event() for _ in range(2)]
-
-    def e2e_loop(n: int) -> float:
-        """Every step: H2D of that step's tokens (prefetched on a copy stream, overlapping the
-        previous step's compute), forward, and a D2H read of the step's result scalar.  The
-        scalar of step i is read on the host while step i+1 is already queued, so the GPU
-        never idles waiting for the host."""
-        for b in range(2):
-            freed[b].record(main)
-        fence(world)
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        stage(0)
-        acc = 0.0
-        for i in range(n):
-            b = i & 1
-            if i + 1 < n:
-                stage(i + 1)                      # prefetch overlaps this step's compute
-            main.wait_event(ready[b])
-            out = layer(bufs[b])
-            freed[b].record(main)
-            result_host[b:b + 1].copy_(torch.linalg.vector_norm(out).reshape(1), non_blocking=True)
-            result_ready[b].record(main)
-            if i > 0:                             # D2H read of the previous step's result
-                result_ready[1 - b].synchronize()
-                acc += float(result_host[1 - b])
-        result_ready[(n - 1) & 1].synchronize()
-        acc += float(result_host[(n - 1) & 1])
-        t1.record()
-        fence(world)
-        return t0.elapsed_time(t1) * 1000.0 / n
-
-    e2e_loop(max(2, min(args.warmup, 3)))
-    e2e_us = max_over_ranks(e2e_loop(args.steps), dev, world)
-    layer.check_status()
-    e2e = {"value": round(e2e_us, 2), "unit": "us",
-           "h2d_bytes_per_step": T * cfg.hidden_dim * 2, "d2h_bytes_per_step": 4,
-           "api": "iris_testing_b200.models.MoELayer.forward"}
-    if launches != layer.launches_per_forward * args.steps:      # counted vs expected: report, do not fail
-        print(f"note: {launches} launches counted, {layer.launches_per_forward * args.steps} expected",
-              file=sys.stderr, flush=True)
-    emit(args, rank, world, us, e2e, launches, clocks,
-         dict(timed="router + plan + dispatch + expert MLP + combine (5 kernels' worth, 6 launches)",
-              capacity_rows=layer.cap_rows), "ours")
+    rc = run_arm(args, arm, cfg, rank, world, local, dev, "ours", count_fn)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return rc
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -307,64 +149,28 @@ def ensure_reference() -> str | None:
     return "baseline/_ref is missing and no reference tree is mounted to install it from"
 
 
-def run_reference(args) -> None:
+def run_reference(args) -> int:
     err = ensure_reference()
     if err is not None:
         print(json.dumps({"impl": "reference", "unavailable": err}), flush=True)
-        return
+        return 0
     sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
     import importlib
     ref_baseline = importlib.import_module("baseline")     # the reference's baseline.py, unmodified
     ref_utils = importlib.import_module("utils")           # the reference's utils.py, unmodified
-    from iris_testing_b200.parallel.baseline_nccl import ReferenceLayerHarness
+    from iris_testing_b200.bench_harness import RefA2AArm, RefLayerArm
 
     rank, world, local, dev = init_dist(args.gpus)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29577")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    h = ReferenceLayerHarness(ref_baseline, ref_utils, args.model, args.batch, args.seq, args.seed,
-                              rank, world, dev)
-    sampler = ClockSampler(local)
-    sampler.start()
-    for i in range(args.warmup):
-        h.step(i & 1)
-    fence(world)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    fence(world)
-    sampler.mark_begin()
-    e0.record()
-    for i in range(args.steps):
-        h.step(i & 1)
-    e1.record()
-    fence(world)
-    sampler.mark_end()
-    us = max_over_ranks(e0.elapsed_time(e1) * 1000.0 / args.steps, dev, world)
-    clocks = sampler.stop()
-
-    # end to end: same loop fed from pinned host memory, result scalar read back every step
-    def e2e_loop(n: int) -> float:
-        fence(world)
-        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0.record()
-        for i in range(n):
-            h.load_from_host(i & 1)
-            y = h.step(i & 1)
-            float(torch.linalg.vector_norm(y).item())
-        t1.record()
-        fence(world)
-        return t0.elapsed_time(t1) * 1000.0 / n
-
-    e2e_loop(2)
-    e2e_us = max_over_ranks(e2e_loop(args.steps), dev, world)
-    e2e = {"value": round(e2e_us, 2), "unit": "us", "h2d_bytes_per_step": h.h2d_bytes,
-           "d2h_bytes_per_step": 4, "api": "reference baseline.run_baseline_ref + torch expert MLP"}
-    emit(args, rank, world, us, e2e, 0, clocks,
-         dict(timed="reference run_baseline_ref (counts + payload all_to_all_single) + torch expert "
-                    "MLP + NCCL return all-to-all + weighted index_add; the reference's Python "
-                    "router/packer runs before the timed region, as in its benchmark.py"),
-         "reference")
+    cfg = make_config(args, world)
+    arm = (RefLayerArm if args.mode == "layer" else RefA2AArm)(ref_baseline, ref_utils, args, rank, world, dev)
+    arm.extra = {"ref_packer": arm.packer}
+    rc = run_arm(args, arm, cfg, rank, world, local, dev, "reference")
     dist.barrier()
     dist.destroy_process_group()
+    return rc
 
 
 def main() -> None:
@@ -373,18 +179,30 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--model", default="mixtral-8x7b")
-    ap.add_argument("--batch", type=int, default=4)
-    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--mode", choices=["layer", "a2a"], default="layer")
+    ap.add_argument("--model", default="mixtral-8x7b", choices=sorted(set(MODEL_DEFAULTS) - {"a2a"}))
+    ap.add_argument("--experts", type=int, default=0, help="experts over the whole EP group (0: the model's)")
+    ap.add_argument("--topk", type=int, default=0, help="0: the model's")
+    ap.add_argument("--batch", type=int, default=0, help="0: the configuration's default")
+    ap.add_argument("--seq", type=int, default=0)
+    ap.add_argument("--hidden", type=int, default=4096, help="a2a mode: token width")
+    ap.add_argument("--combine", action="store_true", help="a2a mode: include the return and the weighted sum")
+    ap.add_argument("--zipf", type=float, default=0.0, help="Zipf exponent of a per-expert router bias (0: none)")
+    ap.add_argument("--zipf-scale", type=float, default=1.0)
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--check-tokens", type=int, default=2048)
+    ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--ref-packer", choices=["auto", "reference", "vectorized"], default="auto",
+                    help="reference arm: its own Python packer, or the same payload built with tensor ops "
+                         "(auto: its own packer up to 65536 routed copies)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    d = MODEL_DEFAULTS["a2a" if args.mode == "a2a" else args.model]
+    args.batch = args.batch or d["batch"]
+    args.seq = args.seq or d["seq"]
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device")
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_ours(args)
+    sys.exit(run_reference(args) if args.impl == "reference" else run_ours(args))
 
 
 if __name__ == "__main__":

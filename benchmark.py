@@ -10,9 +10,11 @@ the device instead of a host clock around prints and a host barrier.
 
 ``MODE`` selects what is measured:
 
-* ``a2a``   (default) padded dispatch (``custom_a2a``) + device barrier  vs the
-            ``all_to_all_single`` baseline; with ``COMBINE=1`` the padded return and the
-            weighted sum are included on both sides.
+* ``a2a``   (default) padded dispatch (``PaddedAllToAll``: the ``custom_a2a`` buffer contract
+            driven by epochs, so no memset or barrier sits between calls) + device-side
+            arrival wait  vs the ``all_to_all_single`` baseline; with ``COMBINE=1`` the padded
+            return and the weighted sum are included on both sides.  ``CAPACITY=0`` sizes the
+            cells from the device-side capacity rule.
 * ``layer`` the fused MoE layer (router + dispatch + experts + combine) vs the same layer
             on library collectives (``AllToAllMoEBaseline``); needs ``FFN`` (0 = single Linear).
             ``TRACE=1`` adds one JSON line per rank: device time of each phase and when
@@ -34,10 +36,8 @@ import torch.distributed as dist
 
 sys.path.insert(0, str(Path(__file__).resolve().parent))
 
-from iris_testing_b200.utils import (alloc_return_buffers, alloc_shmem_buffers, allreduce_max,  # noqa: E402
-                                     allreduce_sum, gen_local_tokens, gen_router, mark, masked_stats,
-                                     reset_dispatch_flags, route_and_pack, sync_and_check,
-                                     zipf_expert_bias)
+from iris_testing_b200.utils import (allreduce_max, allreduce_sum, gen_local_tokens, gen_router,  # noqa: E402
+                                     mark, masked_stats, route_and_pack, sync_and_check, zipf_expert_bias)
 
 
 def env_int(name: str, default: int) -> int:
@@ -66,10 +66,9 @@ def report(rank: int, payload: dict) -> None:
 
 # --------------------------------------------------------------------------- a2a mode
 def run_a2a(rank: int, world: int, dev: torch.device) -> None:
-    from iris_testing_b200.ops import custom_a2a
-    from iris_testing_b200.ops.combine import padded_return, weighted_gather
     from iris_testing_b200.parallel import run_baseline
     from iris_testing_b200.parallel.baseline_nccl import ExchangeBuffers
+    from iris_testing_b200.parallel.padded_a2a import CapacityProbe, PaddedAllToAll
     from iris_testing_b200.parallel.symm import SymmetricHeap
 
     batch, seq, H = env_int("BATCH", 4), env_int("SEQ", 2048), env_int("HIDDEN", 4096)
@@ -84,15 +83,11 @@ def run_a2a(rank: int, world: int, dev: torch.device) -> None:
     x = gen_local_tokens(batch, seq, H, dt, dev, seed, rank, dist_name)
     router = gen_router(H, E, dt, dev, seed, std=None if os.getenv("ROUTER_STD", "") == "" else float(os.environ["ROUTER_STD"]))
     payload, counts, dst_off, _, idx, wgt, plan = route_and_pack(x, router, topk, world, E)
-    gathered = [torch.zeros_like(counts) for _ in range(world)]
-    if world > 1:
-        dist.all_gather(gathered, counts)
-    else:
-        gathered = [counts]
-    counts_all = torch.stack(gathered)                       # [src, dst, e]
-    expected_pca = counts_all[:, rank, :].t().contiguous()   # [e, src]
-    global_max = int(allreduce_max(expected_pca.max().to(torch.int32).reshape(1)).item())
-    pair_max = int(allreduce_max(counts.sum(1).max().to(torch.int32).reshape(1)).item())
+    # CAP (largest cell over all ranks) and M (largest per-pair message) on the device, one read
+    ctl = SymmetricHeap(8 << 20)
+    cap_cell, pair_max, recv_max, _ = CapacityProbe(ctl, e_local).measure(counts.contiguous()).tolist()
+    ctl.close()
+    global_max = int(cap_cell)
     if auto_cap:
         cap = max(global_max, 1)
     if global_max > cap and env_int("SKIP_ON_OVERFLOW", 1):
@@ -103,23 +98,18 @@ def run_a2a(rank: int, world: int, dev: torch.device) -> None:
     need = e_local * world * cap * H * 2 * (2 if combine else 1) + (256 << 20)
     heap_gib = env_int("SYMM_HEAP_GIB", env_int("IRIS_HEAP_GIB", 0))
     heap = SymmetricHeap(max(need, heap_gib << 30))
-    b = alloc_shmem_buffers(heap, world, e_local, cap, H, dt)
-    r = alloc_return_buffers(heap, world, e_local, cap, H, dt) if combine else None
+    a2a = PaddedAllToAll(heap, e_local, cap, H, dt, with_return=bool(combine))
     base = ExchangeBuffers(recv_counts=torch.empty_like(counts))
-    heap.barrier()
 
     def custom_once():
-        reset_dispatch_flags(b, clear_tokens=bool(clear))
+        if clear:
+            a2a.token_buf.zero_()                      # debug aid of the reference (CLEAR_TOKEN_BUF)
+        a2a.dispatch(payload, counts, dst_off)         # flags are re-armed inside the kernel
+        a2a.wait()                                     # device-side: everything for this rank has landed
         if combine:
-            r.ret_sync.zero_()
-        heap.barrier(host_sync=False)                  # every rank's flags are re-armed
-        custom_a2a(payload, counts, dst_off, b.pca, b.token_buf, b.counts_ready, b.token_sync,
-                   b.heap_bases, E, cap)
-        heap.barrier(host_sync=False)                  # all pushes of all ranks have landed
-        if combine:
-            padded_return(b.token_buf, b.pca, r.ret_buf, r.ret_sync, b.heap_bases)
-            return weighted_gather(r.ret_buf, plan, idx, wgt, r.ret_sync, world, cap, status=heap.status)
-        return b.token_buf
+            a2a.send_back()
+            return a2a.reduce(plan, idx, wgt)
+        return a2a.token_buf
 
     def baseline_once():
         _, _, meta = run_baseline(payload, counts, cap, base, do_reorder=False)
@@ -175,11 +165,13 @@ def run_a2a(rank: int, world: int, dev: torch.device) -> None:
     heap.check_status()
     c_ms, b_ms = max_rank_mean(custom_ms, dev), max_rank_mean(base_ms, dev)
     rows_out = int(counts.sum().item())
+    remote = rows_out * H * 2 * (world - 1) / max(world, 1) * (2 if combine else 1)
     report(rank, dict(mode="a2a+combine" if combine else "a2a", world=world, e_local=e_local, cap=cap,
-                      hidden=H, batch=batch, seq=seq, topk=topk, pair_rows_max_M=pair_max,
-                      cell_rows_max=global_max, custom_us=round(c_ms * 1e3, 1),
+                      hidden=H, batch=batch, seq=seq, topk=topk, pair_rows_max_M=int(pair_max),
+                      cell_rows_max=global_max, recv_rows_max=int(recv_max), custom_us=round(c_ms * 1e3, 1),
                       baseline_us=round(b_ms * 1e3, 1), speedup=round(b_ms / c_ms, 3),
                       payload_mb=round(rows_out * H * 2 / 1e6, 2),
+                      nvlink_floor_us=round(remote / 770e9 * 1e6 / (2 if combine else 1), 1),
                       timing="CUDA events, mean over iters, max over ranks"))
     if rank == 0:
         print("=== COMM-only perf (device-timed, max over ranks) ===")
@@ -187,15 +179,18 @@ def run_a2a(rank: int, world: int, dev: torch.device) -> None:
         print(f"custom_ms:   {c_ms:.3f}\nbaseline_ms: {b_ms:.3f}\nspeedup:     {b_ms / c_ms:.3f}x", flush=True)
 
     if check:
-        reset_dispatch_flags(b, clear_tokens=True)
-        heap.barrier()
-        custom_a2a(payload, counts, dst_off, b.pca, b.token_buf, b.counts_ready, b.token_sync,
-                   b.heap_bases, E, cap)
-        heap.barrier()
-        tb, _, _ = run_baseline(payload, counts, cap, ExchangeBuffers(torch.empty_like(counts)),
-                                do_reorder=True)
-        pca_diff = (b.pca - expected_pca).abs().max().float().reshape(1)
-        mx, s1, s2 = masked_stats(b.token_buf, tb, expected_pca)
+        a2a.token_buf.zero_()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        a2a.dispatch(payload, counts, dst_off)
+        a2a.wait()
+        torch.cuda.synchronize()
+        tb, _, meta = run_baseline(payload, counts, cap, ExchangeBuffers(torch.empty_like(counts)),
+                                   do_reorder=True)
+        expected_pca = meta["recv_counts"].t().contiguous()
+        pca_diff = (a2a.pca - expected_pca).abs().max().float().reshape(1)
+        mx, s1, s2 = masked_stats(a2a.token_buf, tb, expected_pca)
         pca_g, mx_g = allreduce_max(pca_diff), allreduce_max(mx.reshape(1))
         s1_g, s2_g = allreduce_sum(s1.reshape(1)), allreduce_sum(s2.reshape(1))
         if rank == 0:
@@ -222,7 +217,9 @@ def run_layer(rank: int, world: int, dev: torch.device) -> None:
     cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=e_local * world, topk=topk, world_size=world,
                     gated=F > 0)
     T = batch * seq
-    heap = SymmetricHeap(heap_bytes_needed(cfg, T) + (64 << 20))
+    need = heap_bytes_needed(cfg, T) + (64 << 20)
+    worst = heap_bytes_needed(cfg, T, cap_rows=world * T * topk) + (64 << 20)
+    heap = SymmetricHeap(need, max_bytes=max(need, worst))          # room to grow after an overflow
     layer = MoELayer(cfg, max_tokens=T, heap=heap, seed=seed, router_std=None)
     zipf = float(os.getenv("ZIPF_S", "0"))
     if zipf > 0:
@@ -232,6 +229,7 @@ def run_layer(rank: int, world: int, dev: torch.device) -> None:
     base = AllToAllMoEBaseline(layer)
     ok, err = True, None
     try:
+        y = layer.forward_checked(x)          # grows the receive buffers if this routing needs it
         for _ in range(warmup):
             y = layer(x)
         torch.cuda.synchronize()
@@ -275,12 +273,22 @@ def run_layer(rank: int, world: int, dev: torch.device) -> None:
     rows = int(layer.group_rows.sum().item())
     rows_max = int(allreduce_max(torch.tensor([rows], device=dev)).item())
     flops = 2.0 * rows_max * D * (3 * F if F > 0 else cfg.out_dim)
-    err_rel = float(((y.float() - yb.float()).abs().max() / yb.float().abs().max().clamp_min(1e-6)).item())
+    scale = yb.float().abs().max().clamp_min(1e-6)
+    row_err = (y.float() - yb.float()).abs().max(dim=1).values / scale
+    err_rel = float(row_err.max().item())
+    # tokens whose top-k choice is a near tie may be routed differently by two correct routers:
+    # report the difference with and without them
+    from iris_testing_b200.ops import cpu_ref
+    clear = cpu_ref.clear_routing_mask(x, layer.router, topk, layer.router_bias)
+    err_clear = float(row_err[clear].max().item()) if bool(clear.any()) else 0.0
     report(rank, dict(mode="layer", world=world, hidden=D, ffn=F, experts=cfg.num_experts, e_local=e_local,
                       topk=topk, batch=batch, seq=seq, zipf_s=zipf, recv_rows_max=rows_max,
                       fused_us=round(ours * 1e3, 1), library_us=round(lib * 1e3, 1),
                       speedup=round(lib / ours, 3), gemm_tflops_at_fused=round(flops / ours / 1e9, 1),
-                      rel_diff_vs_library=round(err_rel, 5),
+                      rel_diff_vs_library=round(err_rel, 5), rel_diff_clear_tokens=round(err_clear, 5),
+                      ambiguous_tokens=int((~clear).sum().item()), capacity_rows=layer.cap_rows,
+                      symmetric_mb=round(layer.memory_bytes()["symmetric"] / 1e6, 1),
+                      local_mb=round(layer.memory_bytes()["local"] / 1e6, 1),
                       timing="CUDA events, mean over iters, max over ranks"))
 
 

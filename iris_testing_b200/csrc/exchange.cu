@@ -126,6 +126,187 @@ __global__ void padded_return_kernel(const uint4* __restrict__ out_buf, const in
   }
 }
 
+// ---------------------------------------------------------------------------
+// Re-usable padded exchange (no memset, no separate barrier between calls).
+//
+// Same buffer contract as above, driven by an epoch number that the host increments per call:
+//  * a rank announces "I have entered epoch i" to every peer only after it has zeroed its own
+//    pca / counts_ready / token_sync (whose previous values its consumer, earlier in the same
+//    stream, is done with); a sender writes into a destination only after it has seen that
+//    announcement, so a fast rank can never write into buffers a slow rank still reads --
+//    the race the reference closes with a memset and a host barrier per call
+//    (benchmark.py:247-272);
+//  * rows move as bulk copies (global -> shared -> the peer's global memory): a tile of a cell is
+//    one contiguous block in the packed payload and in token_buf, so each worker warp streams it
+//    through two 16 KiB buffers and then adds 1 to token_sync[expert] on the destination (per-tile
+//    completion rule, kernels.py:136-146).
+// `mirror` selects the return direction: tiles of out_buf[e, src] go to ret_buf[rank, e] on src
+// and are counted in ret_sync[rank] there (no announcement is needed: a return follows the
+// dispatch it answers).
+// ---------------------------------------------------------------------------
+constexpr int A2A_WARPS = 4;
+constexpr int A2A_CHUNK = 16384;
+
+struct PaddedArgs {
+  PeerTable pca, token_buf, counts_ready, token_sync, entered;   // dispatch; mirror: token_buf = ret_buf,
+                                                                 // token_sync = ret_sync
+  const uint32_t* entered_local;   // [world] on this rank: epochs the peers have entered
+  uint32_t epoch;
+  int rank, world, e_local, cap, block_m;
+  long long row_bytes;
+  int mirror;
+  int* status;
+  unsigned long long budget_ns;
+};
+
+__global__ void __launch_bounds__(A2A_WARPS * 32)
+padded_bulk_kernel(const uint8_t* __restrict__ src_rows, const int* __restrict__ counts,
+                   const int* __restrict__ dst_offsets, PaddedArgs a) {
+  extern __shared__ __align__(128) uint8_t a2a_smem[];
+  __shared__ uint64_t bars[A2A_WARPS][2];
+  __shared__ int s_abort;
+  __shared__ int s_eoff[B200_MAX_EXPERTS];     // dispatch: first payload row of cell (dst, e)
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int W = a.world, EL = a.e_local;
+  if (tid == 0) s_abort = 0;
+  if (lane == 0) {
+    mbar_init(&bars[warp][0], 1);
+    mbar_init(&bars[warp][1], 1);
+    fence_mbar_init();
+  }
+  if (!a.mirror) {
+    for (int c = tid; c < W * EL; c += blockDim.x) {
+      const int d = c / EL, e = c - d * EL;
+      int off = dst_offsets[d];
+      for (int e2 = 0; e2 < e; ++e2) off += counts[d * EL + e2];
+      s_eoff[c] = off;
+    }
+  }
+  __syncthreads();
+  WaitCtx w; w.abort_flag = &s_abort; w.status = a.status; w.budget_ns = a.budget_ns;
+
+  if (!a.mirror) {
+    // ---- announce this epoch (after re-arming the local flags), then deliver the counts
+    if (blockIdx.x == 0) {
+      int* pca = reinterpret_cast<int*>(a.pca.p[a.rank]);
+      for (int i = tid; i < EL * W; i += blockDim.x) pca[i] = 0;
+      for (int e = tid; e < EL; e += blockDim.x) reinterpret_cast<uint32_t*>(a.token_sync.p[a.rank])[e] = 0u;
+      if (tid == 0) *reinterpret_cast<uint32_t*>(a.counts_ready.p[a.rank]) = 0u;
+      __syncthreads();
+      if (tid < W) {
+        fence_acq_rel_sys();
+        st_release_sys(reinterpret_cast<uint32_t*>(a.entered.p[tid]) + a.rank, a.epoch);
+      }
+    }
+    for (int d = blockIdx.x; d < W; d += gridDim.x) {
+      const int dst = (a.rank + d) % W;
+      if (tid == 0) wait_flag_geq(a.entered_local + dst, a.epoch, w, ST_TIMEOUT_BARRIER);
+      __syncthreads();
+      if (!s_abort) {
+        int* pca = reinterpret_cast<int*>(a.pca.p[dst]);
+        for (int e = tid; e < EL; e += blockDim.x) pca[e * W + a.rank] = counts[dst * EL + e];
+      }
+      __syncthreads();
+      if (tid == 0 && !s_abort) {
+        fence_acq_rel_sys();
+        red_add_release_sys(reinterpret_cast<uint32_t*>(a.counts_ready.p[dst]), 1u);
+      }
+    }
+  }
+
+  // ---- tiles: one worker warp per unit, lane 0 drives the bulk copies
+  if (lane != 0) return;
+  uint8_t* buf[2] = {a2a_smem + (warp * 2) * A2A_CHUNK, a2a_smem + (warp * 2 + 1) * A2A_CHUNK};
+  uint32_t phase[2] = {0u, 0u};
+  unsigned entered_ok = a.mirror ? 0xffffffffu : 0u;
+  const int tpc = (a.cap + a.block_m - 1) / a.block_m;
+  const long long total = static_cast<long long>(W) * EL * tpc;
+  const long long worker = static_cast<long long>(blockIdx.x) * A2A_WARPS + warp;
+  const long long nworkers = static_cast<long long>(gridDim.x) * A2A_WARPS;
+  for (long long u = worker; u < total; u += nworkers) {
+    // the peer index runs fastest, rotated by rank: at any moment all links are in use and
+    // the ranks target different peers
+    const int d = static_cast<int>(u % W);
+    const long long rest = u / W;
+    const int e = static_cast<int>(rest % EL), mt = static_cast<int>(rest / EL);
+    const int peer = (a.rank + d) % W;
+    const int n_true = a.mirror ? __ldcg(counts + e * W + peer) : counts[peer * EL + e];
+    if (n_true > a.cap && mt == 0) report_status(a.status, ST_OVERFLOW);
+    const int n = min(n_true, a.cap);             // rows beyond the cell's capacity are dropped
+    const int m0 = mt * a.block_m;
+    if (m0 >= n) continue;                        // empty tile: nothing to send, nothing to signal
+    const int rows = min(a.block_m, n - m0);
+    if (!(entered_ok >> peer & 1u)) {
+      if (!wait_flag_geq(a.entered_local + peer, a.epoch, w, ST_TIMEOUT_BARRIER)) break;
+      entered_ok |= 1u << peer;
+    }
+    const uint8_t* src;
+    uint8_t* dst;
+    if (!a.mirror) {
+      src = src_rows + (static_cast<long long>(s_eoff[peer * EL + e]) + m0) * a.row_bytes;
+      dst = reinterpret_cast<uint8_t*>(a.token_buf.p[peer]) +
+            ((static_cast<long long>(e) * W + a.rank) * a.cap + m0) * a.row_bytes;
+    } else {
+      src = src_rows + ((static_cast<long long>(e) * W + peer) * a.cap + m0) * a.row_bytes;
+      dst = reinterpret_cast<uint8_t*>(a.token_buf.p[peer]) +
+            ((static_cast<long long>(a.rank) * EL + e) * a.cap + m0) * a.row_bytes;
+    }
+    const long long bytes = rows * a.row_bytes;
+    const int nchunks = static_cast<int>((bytes + A2A_CHUNK - 1) / A2A_CHUNK);
+    bool ok = true;
+    {
+      const uint32_t sz = static_cast<uint32_t>(min(static_cast<long long>(A2A_CHUNK), bytes));
+      mbar_expect_tx(&bars[warp][0], sz);
+      bulk_load_1d(buf[0], src, sz, &bars[warp][0]);
+    }
+    for (int c = 0; c < nchunks && ok; ++c) {
+      const int b = c & 1;
+      const long long off = static_cast<long long>(c) * A2A_CHUNK;
+      const uint32_t sz = static_cast<uint32_t>(min(static_cast<long long>(A2A_CHUNK), bytes - off));
+      if (c + 1 < nchunks) {
+        // the other buffer's previous store (chunk c-1) must have been read before it is refilled
+        bulk_wait_group_read<0>();
+        const long long off2 = off + A2A_CHUNK;
+        const uint32_t sz2 = static_cast<uint32_t>(min(static_cast<long long>(A2A_CHUNK), bytes - off2));
+        mbar_expect_tx(&bars[warp][b ^ 1], sz2);
+        bulk_load_1d(buf[b ^ 1], src + off2, sz2, &bars[warp][b ^ 1]);
+      }
+      ok = mbar_wait(&bars[warp][b], phase[b], w, ST_TIMEOUT_PIPE_FULL);
+      phase[b] ^= 1u;
+      if (!ok) break;
+      bulk_store_1d(dst + off, buf[b], sz);
+      bulk_commit_group();
+    }
+    // the tile's rows are in the peer's memory before its arrival is counted there
+    bulk_wait_group<0>();
+    if (!ok) break;
+    fence_proxy_async();
+    fence_acq_rel_sys();
+    uint32_t* flag = reinterpret_cast<uint32_t*>(a.token_sync.p[peer]) + (a.mirror ? a.rank : e);
+    red_add_release_sys(flag, 1u);
+  }
+  bulk_wait_group<0>();
+}
+
+// Waits (bounded) until a dispatch has fully landed on this rank: counts_ready == world and
+// token_sync[e] == sum_src ceil(min(pca[e, src], cap) / block_m).  The device-side counterpart
+// of the host spin-waits of unit_tests.py:17-43; replaces a cross-rank barrier after the call.
+__global__ void padded_wait_kernel(const int* pca, const uint32_t* counts_ready, const uint32_t* token_sync,
+                                   int world, int e_local, int cap, int block_m, int* status,
+                                   unsigned long long budget_ns) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  __syncthreads();
+  WaitCtx w; w.abort_flag = &s_abort; w.status = status; w.budget_ns = budget_ns;
+  if (threadIdx.x == 0) wait_flag_geq(counts_ready, static_cast<uint32_t>(world), w, ST_TIMEOUT_COUNTS);
+  __syncthreads();
+  for (int e = threadIdx.x; e < e_local && !s_abort; e += blockDim.x) {
+    uint32_t expect = 0;
+    for (int s = 0; s < world; ++s) expect += (min(__ldcg(pca + e * world + s), cap) + block_m - 1) / block_m;
+    wait_flag_geq(token_sync + e, expect, w, ST_TIMEOUT_TILE_READY);
+  }
+}
+
 // y[t, :] = sum_slot w[t, slot] * ret_buf[cell(t, slot), :] -- the top-k
 // weighted sum on the source rank.  dst_slot[t*k+slot] is the payload row of
 // that copy; bucket_start / send_counts locate its (dst, e, m) cell.
@@ -134,12 +315,13 @@ __global__ void weighted_gather_kernel(const __nv_bfloat16* __restrict__ ret_buf
                                        const int* __restrict__ dst_slot,
                                        const int* __restrict__ topk_idx,
                                        const int* __restrict__ bucket_start,
-                                       const float* __restrict__ topk_w, const uint32_t* ret_sync,
+                                       const float* __restrict__ topk_w, uint32_t* ret_sync,
                                        const int* __restrict__ send_counts, int T, int topk, int world,
                                        int e_local, int cap, int H, int block_m,
                                        __nv_bfloat16* __restrict__ y, int* status,
-                                       unsigned long long budget_ns) {
+                                       unsigned long long budget_ns, unsigned int* ticket) {
   __shared__ int s_abort;
+  __shared__ int s_last;
   if (threadIdx.x == 0) s_abort = 0;
   __syncthreads();
   if (threadIdx.x < world) {
@@ -150,10 +332,9 @@ __global__ void weighted_gather_kernel(const __nv_bfloat16* __restrict__ ret_buf
     wait_flag_geq(ret_sync + threadIdx.x, expect, w, ST_TIMEOUT_COMBINE);
   }
   __syncthreads();
-  if (s_abort) return;
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int nwarps = (gridDim.x * blockDim.x) >> 5;
-  for (int t = warp; t < T; t += nwarps) {
+  for (int t = warp; t < T && !s_abort; t += nwarps) {
     for (int c0 = lane * 8; c0 < H; c0 += 256) {
       float acc[8];
 #pragma unroll
@@ -178,6 +359,21 @@ __global__ void weighted_gather_kernel(const __nv_bfloat16* __restrict__ ret_buf
       o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
       o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
       *reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * H + c0) = o;
+    }
+  }
+  // With a ticket counter the last block re-arms ret_sync for the next exchange: every block
+  // has seen all of this exchange's arrivals, and the next return cannot start before this
+  // rank's next dispatch, which follows this kernel in its stream.
+  if (ticket != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      s_last = (atomicAdd(ticket, 1u) == gridDim.x - 1) ? 1 : 0;
+    }
+    __syncthreads();
+    if (s_last) {
+      if (threadIdx.x < world) ret_sync[threadIdx.x] = 0u;
+      if (threadIdx.x == 0) *ticket = 0u;
     }
   }
 }
@@ -428,19 +624,75 @@ int b200_padded_return(const void* out_buf, const int* pca, const unsigned long 
   return static_cast<int>(cudaGetLastError());
 }
 
+// Epoch-driven padded dispatch (mirror = 0) or return (mirror = 1); see padded_bulk_kernel.
+// dispatch: rows = packed payload, counts = send_counts [world, e_local], dst_offsets [world];
+// return:   rows = out_buf [e_local, world, cap, H], counts = pca [e_local, world], dst_offsets unused,
+//           peer_token_buf = ret_buf, peer_token_sync = ret_sync.
+int b200_padded_exchange(const void* rows, const int* counts, const int* dst_offsets,
+                         const unsigned long long* peer_pca, const unsigned long long* peer_token_buf,
+                         const unsigned long long* peer_counts_ready,
+                         const unsigned long long* peer_token_sync,
+                         const unsigned long long* peer_entered, const void* entered_local,
+                         unsigned int epoch, int rank, int world, int e_local, int cap, int hidden_dim,
+                         int elem_bytes, int block_m, int mirror, int num_blocks, int* status,
+                         unsigned long long budget_ns, void* stream) {
+  if (world < 1 || world > B200_MAX_WORLD || world * e_local > B200_MAX_EXPERTS || block_m < 1 || cap < 1 ||
+      (static_cast<long long>(hidden_dim) * elem_bytes) % 16 != 0 || num_blocks < 1 ||
+      (reinterpret_cast<uintptr_t>(rows) & 15u) != 0)
+    return -1;
+  static bool configured = false;
+  const int smem = b200::A2A_WARPS * 2 * b200::A2A_CHUNK;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(b200::padded_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  b200::PaddedArgs a;
+  memset(&a, 0, sizeof(a));
+  if (!mirror) {
+    a.pca = make_table(peer_pca, world);
+    a.counts_ready = make_table(peer_counts_ready, world);
+    a.entered = make_table(peer_entered, world);
+    a.entered_local = static_cast<const uint32_t*>(entered_local);
+  }
+  a.token_buf = make_table(peer_token_buf, world);
+  a.token_sync = make_table(peer_token_sync, world);
+  a.epoch = epoch;
+  a.rank = rank; a.world = world; a.e_local = e_local; a.cap = cap; a.block_m = block_m;
+  a.row_bytes = static_cast<long long>(hidden_dim) * elem_bytes;
+  a.mirror = mirror;
+  a.status = status;
+  a.budget_ns = budget_ns;
+  b200::padded_bulk_kernel<<<num_blocks, b200::A2A_WARPS * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(rows), counts, dst_offsets, a);
+  b200_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int b200_padded_wait(const int* pca, const void* counts_ready, const void* token_sync, int world,
+                     int e_local, int cap, int block_m, int* status, unsigned long long budget_ns,
+                     void* stream) {
+  if (world < 1 || e_local < 1 || block_m < 1) return -1;
+  b200::padded_wait_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      pca, static_cast<const uint32_t*>(counts_ready), static_cast<const uint32_t*>(token_sync), world,
+      e_local, cap, block_m, status, budget_ns);
+  b200_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
 int b200_weighted_gather(const void* ret_buf, const int* dst_slot, const int* topk_idx,
-                         const int* bucket_start, const float* topk_w, const void* ret_sync,
+                         const int* bucket_start, const float* topk_w, void* ret_sync,
                          const int* send_counts, int T, int topk, int world, int e_local, int cap,
                          int hidden_dim, int block_m, void* y, int* status,
-                         unsigned long long budget_ns, void* stream) {
+                         unsigned long long budget_ns, unsigned int* ticket, void* stream) {
   if (hidden_dim % 8 != 0 || world > 32) return -1;
   int blocks = (T + 7) / 8;
   if (blocks < 1) blocks = 1;
   if (blocks > 148 * 8) blocks = 148 * 8;
   b200::weighted_gather_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(ret_buf), dst_slot, topk_idx, bucket_start, topk_w,
-      static_cast<const uint32_t*>(ret_sync), send_counts, T, topk, world, e_local, cap, hidden_dim,
-      block_m, static_cast<__nv_bfloat16*>(y), status, budget_ns);
+      static_cast<uint32_t*>(ret_sync), send_counts, T, topk, world, e_local, cap, hidden_dim,
+      block_m, static_cast<__nv_bfloat16*>(y), status, budget_ns, ticket);
   b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

@@ -212,6 +212,74 @@ __global__ void plan_finalize_kernel(const int* __restrict__ topk_idx,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Capacity of a padded exchange, computed on the device across all ranks (no host round
+// trip).  Every rank pushes its send_counts row ([dst][e]) into slot [rank] of a table on
+// every peer and stamps a flag with the epoch; once all flags show the epoch, each rank
+// reduces the full [src][dst][e] table to
+//   out[0] = CAP: the largest (src, dst, expert) cell -- the rule of utils.py:118-121,
+//   out[1] = M:   the most rows any rank sends to any one rank -- the fixed message size of
+//                 README.md:5-7 (every pair sends M rows, zero padded),
+//   out[2] = the most rows any rank receives (what a receive buffer must hold),
+//   out[3] = the rows this rank receives.
+// Tables and flags are double-buffered by epoch parity: a rank can be at most one epoch
+// ahead of the slowest reader (it cannot finish an epoch before everyone has pushed it).
+// ---------------------------------------------------------------------------
+struct CapacityArgs {
+  int world, rank, e_local;
+  uint32_t epoch;
+  unsigned long long peer_table[B200_MAX_WORLD];   // int [2][world][world * e_local] on each rank
+  unsigned long long peer_flags[B200_MAX_WORLD];   // uint32 [2][world] on each rank
+  int* status;
+  unsigned long long budget_ns;
+};
+
+__global__ void capacity_kernel(const int* __restrict__ send_counts, CapacityArgs a, int* __restrict__ out) {
+  __shared__ int s_abort;
+  __shared__ int s_red[4];
+  const int W = a.world, EL = a.e_local, ET = W * EL, tid = threadIdx.x;
+  const unsigned par = a.epoch & 1u;
+  if (tid == 0) { s_abort = 0; s_red[0] = s_red[1] = s_red[2] = s_red[3] = 0; }
+  __syncthreads();
+  for (int p = 0; p < W; ++p) {
+    int* row = reinterpret_cast<int*>(a.peer_table[p]) + (static_cast<size_t>(par) * W + a.rank) * ET;
+    for (int i = tid; i < ET; i += blockDim.x) row[i] = send_counts[i];
+  }
+  __syncthreads();
+  WaitCtx w; w.abort_flag = &s_abort; w.status = a.status; w.budget_ns = a.budget_ns;
+  if (tid < W) {
+    fence_acq_rel_sys();
+    st_release_sys(reinterpret_cast<uint32_t*>(a.peer_flags[tid]) + par * W + a.rank, a.epoch);
+    wait_flag_geq(reinterpret_cast<const uint32_t*>(a.peer_flags[a.rank]) + par * W + tid, a.epoch, w,
+                  ST_TIMEOUT_COUNTS);
+  }
+  __syncthreads();
+  if (s_abort) return;
+  const int* tab = reinterpret_cast<const int*>(a.peer_table[a.rank]) + static_cast<size_t>(par) * W * ET;
+  // one thread per (src, dst) pair
+  for (int pr = tid; pr < W * W; pr += blockDim.x) {
+    const int src = pr / W, dst = pr - src * W;
+    int cell = 0, pair = 0;
+    for (int e = 0; e < EL; ++e) {
+      const int c = __ldcg(tab + (src * W + dst) * EL + e);
+      cell = max(cell, c);
+      pair += c;
+    }
+    atomicMax(&s_red[0], cell);
+    atomicMax(&s_red[1], pair);
+  }
+  __syncthreads();
+  for (int dst = tid; dst < W; dst += blockDim.x) {
+    int recv = 0;
+    for (int src = 0; src < W; ++src)
+      for (int e = 0; e < EL; ++e) recv += __ldcg(tab + (src * W + dst) * EL + e);
+    atomicMax(&s_red[2], recv);
+    if (dst == a.rank) s_red[3] = recv;
+  }
+  __syncthreads();
+  if (tid < 4) out[tid] = s_red[tid];
+}
+
 // Gathers the packed send payload: payload[j, :] = x[send_order[j] / topk, :].
 __global__ void pack_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ send_order,
                                  int n_flat, int topk, int row16, uint4* __restrict__ payload) {
@@ -280,6 +348,17 @@ int b200_pack_rows(const void* x, const int* send_order, int n_flat, int topk, i
 }
 
 }  // extern "C"
+
+extern "C" int b200_capacity(const int* send_counts, const b200::CapacityArgs* a, int* out, void* stream) {
+  if (a == nullptr || a->world < 1 || a->world > B200_MAX_WORLD || a->e_local < 1 ||
+      a->world * a->e_local > B200_MAX_EXPERTS || a->rank < 0 || a->rank >= a->world || a->epoch == 0)
+    return -1;
+  b200::capacity_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>(send_counts, *a, out);
+  b200_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int b200_abi_size_capacity_args() { return static_cast<int>(sizeof(b200::CapacityArgs)); }
 
 extern "C" int b200_abi_size_plan_push_args() { return static_cast<int>(sizeof(b200::PlanPushArgs)); }
 

@@ -47,12 +47,14 @@ def padded_return(out_buf: torch.Tensor, pca: torch.Tensor, ret_buf: torch.Tenso
 
 def weighted_gather(ret_buf: torch.Tensor, plan, topk_idx: torch.Tensor, topk_w: torch.Tensor,
                     ret_sync: Optional[torch.Tensor], world: int, capacity: int,
-                    status: Optional[torch.Tensor] = None, wait_budget_ms: float = 2000.0
-                    ) -> torch.Tensor:
+                    status: Optional[torch.Tensor] = None, wait_budget_ms: float = 2000.0,
+                    rearm_ticket: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[t] = sum_slot topk_w[t, slot] * ret_buf[cell of (t, slot)]   -> [T, H].
 
     ``plan`` is the :class:`~iris_testing_b200.ops.plan.Plan` used for the dispatch.  On CUDA
-    the kernel first waits (bounded) until ``ret_sync`` shows every returned tile."""
+    the kernel first waits (bounded) until ``ret_sync`` shows every returned tile; with
+    ``rearm_ticket`` (an int32 scratch counter that is zero between calls) it also zeroes
+    ``ret_sync`` when done, so the next exchange needs no memset."""
     T, k = topk_idx.shape
     H = ret_buf.shape[-1]
     e_local = ret_buf.shape[1]
@@ -66,7 +68,7 @@ def weighted_gather(ret_buf: torch.Tensor, plan, topk_idx: torch.Tensor, topk_w:
     fn = declare("b200_weighted_gather",
                  [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                   C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
-                  C.c_void_p, C.c_ulonglong, C.c_void_p])
+                  C.c_void_p, C.c_ulonglong, C.c_void_p, C.c_void_p])
     y = torch.empty((T, H), dtype=ret_buf.dtype, device=ret_buf.device)
     if status is None:
         status = default_status(ret_buf.device)
@@ -74,6 +76,6 @@ def weighted_gather(ret_buf: torch.Tensor, plan, topk_idx: torch.Tensor, topk_w:
         ret_sync = torch.full((world,), 2 ** 30, dtype=torch.int32, device=ret_buf.device)
     rc = fn(ptr(ret_buf), ptr(plan.dst_slot), ptr(topk_idx), ptr(plan.bucket_start), ptr(topk_w),
             ptr(ret_sync), ptr(plan.counts), T, k, world, e_local, capacity, H, tile_rows(), ptr(y),
-            ptr(status), int(wait_budget_ms * 1e6), stream_ptr(ret_buf))
+            ptr(status), int(wait_budget_ms * 1e6), ptr(rearm_ticket), stream_ptr(ret_buf))
     nv.check(rc, "weighted gather launch")
     return y

@@ -158,13 +158,15 @@ def dense_moe_ref(x: torch.Tensor, w_router: torch.Tensor, topk: int, *,
                   w1: Optional[torch.Tensor] = None, w3: Optional[torch.Tensor] = None,
                   w2: Optional[torch.Tensor] = None, w_single: Optional[torch.Tensor] = None,
                   bias: Optional[torch.Tensor] = None, renormalize: bool = False,
-                  round_hidden: Optional[torch.dtype] = None) -> torch.Tensor:
+                  round_hidden: Optional[torch.dtype] = None,
+                  routing: Optional[Tuple[torch.Tensor, torch.Tensor]] = None) -> torch.Tensor:
     """Single-process dense MoE layer over ALL experts (fp32).
 
     Gated: w1, w3 [E, D, F], w2 [E, F, D].  Single Linear: w_single [E, D, N].
     y[t] = sum_slot weight[t, slot] * expert_{idx[t, slot]}(x[t]).
+    ``routing`` = (idx [T, k], weight [T, k]) replaces the oracle's own router.
     """
-    idx, wgt = router_topk_ref(x, w_router, topk, bias, renormalize)
+    idx, wgt = routing if routing is not None else router_topk_ref(x, w_router, topk, bias, renormalize)
     E = (w1 if w1 is not None else w_single).shape[0]
     out_dim = w2.shape[2] if w2 is not None else w_single.shape[2]
     y = torch.zeros(x.shape[0], out_dim, dtype=torch.float32, device=x.device)
@@ -191,3 +193,38 @@ def interleave_gate_up(w1: torch.Tensor, w3: torch.Tensor, block: int = 128) -> 
     g = w1.transpose(1, 2).reshape(E, Fdim // block, 1, block, D)
     u = w3.transpose(1, 2).reshape(E, Fdim // block, 1, block, D)
     return torch.cat([g, u], dim=2).reshape(E, 2 * Fdim, D).contiguous()
+
+
+def clear_routing_mask(x: torch.Tensor, w_router: torch.Tensor, topk: int,
+                       bias: Optional[torch.Tensor] = None, min_gap: float = 1e-6) -> torch.Tensor:
+    """bool [T]: tokens whose top-k choice is unambiguous -- every gap between consecutive sorted
+    probabilities down to the (k+1)-th exceeds ``min_gap``.  On the other tokens two correct
+    routers may legitimately pick different experts (or order them differently)."""
+    logits = x.float() @ w_router.float()
+    if bias is not None:
+        logits = logits + bias.float()
+    srt = torch.sort(F.softmax(logits, dim=-1), dim=-1, descending=True).values
+    if srt.shape[1] <= topk:
+        return torch.ones(x.shape[0], dtype=torch.bool, device=x.device)
+    return (srt[:, :topk] - srt[:, 1:topk + 1]).min(dim=1).values > min_gap
+
+
+def compare_with_dense(y: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, topk: int, kernel_idx,
+                       *, bias=None, renormalize: bool = False, tol: float = 1e-2, **weights) -> dict:
+    """Compare a layer output with :func:`dense_moe_ref`, tokens with an ambiguous top-k set aside.
+
+    Returns ``max_rel_err`` (largest |y - ref| over the clear tokens, relative to max |ref|),
+    the same over all tokens, the number of ambiguous tokens, whether the kernel's expert sets
+    equal the oracle's on every clear token, and ``ok``."""
+    ref = dense_moe_ref(x, w_router, topk, bias=bias, renormalize=renormalize, **weights)
+    clear = clear_routing_mask(x, w_router, topk, bias)
+    ridx, _ = router_topk_ref(x, w_router, topk, bias, renormalize)
+    same = (torch.sort(kernel_idx.long(), dim=1).values == torch.sort(ridx.long(), dim=1).values).all(dim=1)
+    scale = float(ref.abs().max().clamp_min(1e-20))
+    diff = (y.float() - ref).abs().max(dim=1).values if y.numel() else torch.zeros(0, device=y.device)
+    err_clear = float(diff[clear].max()) / scale if bool(clear.any()) else 0.0
+    err_all = float(diff.max()) / scale if diff.numel() else 0.0
+    routing_ok = bool(same[clear].all()) if bool(clear.any()) else True
+    return dict(max_rel_err=err_clear, max_rel_err_all_tokens=err_all, ambiguous_tokens=int((~clear).sum()),
+                tokens=int(x.shape[0]), routing_ok=routing_ok, tol=tol,
+                ok=bool(routing_ok and err_clear <= tol))

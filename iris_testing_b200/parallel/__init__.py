@@ -11,3 +11,15 @@ def SymmetricHeap(*args, **kwargs):
     """Lazy constructor: the native library is only touched when a heap is made."""
     from .symm import SymmetricHeap as _H
     return _H(*args, **kwargs)
+
+
+def PaddedAllToAll(*args, **kwargs):
+    """Lazy constructor of :class:`iris_testing_b200.parallel.padded_a2a.PaddedAllToAll`."""
+    from .padded_a2a import PaddedAllToAll as _P
+    return _P(*args, **kwargs)
+
+
+def CapacityProbe(*args, **kwargs):
+    """Lazy constructor of :class:`iris_testing_b200.parallel.padded_a2a.CapacityProbe`."""
+    from .padded_a2a import CapacityProbe as _C
+    return _C(*args, **kwargs)

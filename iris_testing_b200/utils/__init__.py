@@ -7,7 +7,8 @@ from .compare import (all_ranks_ok, allreduce_max, allreduce_min, allreduce_sum,
                       sync_and_check)
 from .gen import (gen_gated_expert_weights, gen_local_tokens, gen_local_weights, gen_router,
                   set_seed, zipf_expert_bias)
-from .pack import (build_dst_offsets, build_expert_offsets, compute_capacity_from_pca,
+from .pack import (build_dst_offsets, build_expert_offsets, compute_capacity_device,
+                   compute_capacity_from_pca,
                    route_and_pack, route_and_pack_padding_free)
 from .waits import (WaitTimeout, expected_tiles, mark, spin_wait_counts_ready,
                     spin_wait_token_sync)

@@ -62,3 +62,13 @@ def compute_capacity_from_pca(pca: torch.Tensor, group=None) -> int:
     if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
         dist.all_reduce(cap, op=dist.ReduceOp.MAX, group=group)
     return max(int(cap.item()), 1)
+
+
+def compute_capacity_device(probe, send_counts: torch.Tensor) -> torch.Tensor:
+    """Device-side capacity rule: int32 ``[CAP, M, max rows received, rows received here]``.
+
+    ``CAP`` is the rule above (largest cell over all ranks), ``M`` the README's message size
+    (largest number of rows any rank sends to any one rank, README.md:5-7).  ``probe`` is a
+    :class:`~iris_testing_b200.parallel.padded_a2a.CapacityProbe`; nothing is copied to the
+    host, so the result can size later launches from a graph or be read once with ``.tolist()``."""
+    return probe.measure(send_counts.contiguous())

@@ -214,3 +214,75 @@ def test_heap_barrier_and_bounded_wait(dev, heap):
     shuffle(buf, pca, never, ready, status=status, wait_budget_ms=50)
     torch.cuda.synchronize()
     assert status[0].item() == 6     # "a dispatched token tile never arrived"
+
+
+def test_device_row_counts_beyond_the_buffers_are_reported_not_stored(dev):
+    """Row counts are read on the device; counts that add up to more rows than a buffer holds
+    must end in a status code, never in a store past the buffer."""
+    from iris_testing_b200.ops import check_default_status, default_status, grouped_gemm, shuffle
+    a = torch.randn(256, 128, device=dev).to(torch.bfloat16)
+    w = torch.randn(2, 256, 128, device=dev).to(torch.bfloat16)
+    out = torch.zeros(256 + 64, 256, dtype=torch.bfloat16, device=dev)       # 64 guard rows behind the output
+    rows = torch.tensor([200, 200], dtype=torch.int32, device=dev)           # 400 > 256
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    grouped_gemm(a, w, rows, out=out[:256], status=status)
+    torch.cuda.synchronize()
+    assert status.tolist()[:2] == [10, 400] and float(out.abs().sum()) == 0.0
+    # same call without a status tensor: the report lands in the device's default status word
+    default_status(dev).zero_()
+    grouped_gemm(a, w, rows, out=out[:256])
+    with pytest.raises(Exception, match=r"overflow.*rows needed: 400"):
+        check_default_status(dev)
+    check_default_status(dev)                                                # reset by the failed check
+    # shuffle into a packed buffer that is too small: the copy stops at max_rows
+    pca = torch.tensor([[6], [5]], dtype=torch.int32, device=dev)
+    buf = torch.ones(2, 1, 8, 64, dtype=torch.bfloat16, device=dev)
+    st2 = torch.zeros(4, dtype=torch.int32, device=dev)
+    packed, _ = shuffle(buf, pca, max_rows=8, status=st2)
+    torch.cuda.synchronize()
+    assert packed.shape[0] == 8 and st2.tolist()[:2] == [10, 11]
+
+
+@pytest.mark.parametrize("e_local,H,T,k,combine", [(2, 128, 100, 2, False), (8, 4096, 1024, 2, True),
+                                                   (4, 768, 777, 4, True), (1, 264, 50, 1, True)])
+def test_padded_all_to_all_engine_repeats_without_memsets(dev, e_local, H, T, k, combine):
+    """``PaddedAllToAll`` on a world of one, three exchanges in a row with changing routing: flags
+    re-armed in-kernel, valid rows bit-equal to the payload, padding never written, and with
+    the return path the weighted sum of the rows that come home."""
+    from iris_testing_b200.parallel.padded_a2a import CapacityProbe, PaddedAllToAll
+    from iris_testing_b200.parallel.symm import SymmetricHeap
+    from iris_testing_b200.utils import gen_local_tokens, gen_router, route_and_pack
+    E = e_local
+    heap = SymmetricHeap(64 << 20, max_bytes=1 << 30)
+    probe = CapacityProbe(heap, e_local)
+    router = gen_router(H, E, torch.bfloat16, dev, 3, std=None)
+    xs = [gen_local_tokens(1, T, H, torch.bfloat16, dev, s, 0, "normal") for s in range(3)]
+    routed = [route_and_pack(x, router, k, 1, E) for x in xs]
+    caps = torch.stack([probe.measure(r[1].contiguous()) for r in routed]).tolist()
+    for c, r in zip(caps, routed):
+        n = r[1].to(torch.int64)
+        assert c == [int(n.max()), int(n.sum()), int(n.sum()), int(n.sum())]     # CAP, M, rows received
+    cap = max(c[0] for c in caps)
+    a2a = PaddedAllToAll(heap, e_local, cap, H, torch.bfloat16, with_return=combine)
+    a2a.token_buf.fill_(7.0)                                  # padding must stay whatever it was
+    for x, (payload, counts, dst_off, _, idx, wgt, plan) in zip(xs, routed):
+        out = a2a.dispatch(payload, counts, dst_off)
+        a2a.wait()
+        torch.cuda.synchronize()
+        assert torch.equal(a2a.pca, counts.t()) and int(a2a.counts_ready[0]) == 1
+        tiles = ((counts.reshape(-1) + 31) // 32).to(torch.int32)
+        assert torch.equal(a2a.token_sync, tiles)
+        off = 0
+        for e, n in enumerate(counts.reshape(-1).tolist()):
+            assert torch.equal(out[e, 0, :n], payload[off:off + n]), e
+            off += n
+        if combine:
+            a2a.send_back()
+            y = a2a.reduce(plan, idx, wgt)
+            ref = x.float() * wgt.sum(dim=1, keepdim=True)
+            assert torch.allclose(y.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2)
+            torch.cuda.synchronize()
+            assert int(a2a.ret.ret_sync.abs().sum()) == 0     # re-armed by the reduce
+    heap.check_status()
+    del a2a, probe
+    heap.close()

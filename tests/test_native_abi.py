@@ -26,6 +26,9 @@ def test_argument_block_sizes_match():
     lib.b200_abi_size_plan_push_args.restype = C.c_int
     assert lib.b200_abi_size_retire_args() == C.sizeof(RetireArgs)
     assert lib.b200_abi_size_plan_push_args() == C.sizeof(PlanPushArgs)
+    from iris_testing_b200.parallel.padded_a2a import _CapacityArgs
+    lib.b200_abi_size_capacity_args.restype = C.c_int
+    assert lib.b200_abi_size_capacity_args() == C.sizeof(_CapacityArgs)
 
 
 def test_limits_agree():
