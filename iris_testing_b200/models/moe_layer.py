@@ -135,6 +135,11 @@ class MoELayer(nn.Module):
         self._num_ctas = num_ctas       # persistent grid of the GEMM kernels (default: one CTA per SM)
         self._debug_canaries = bool(debug_canaries)
         self._canaries = []
+        # L2 eviction-priority hints of the two GEMM kernels (bit 0: keep activations, bit 1: stream
+        # weights, bit 2: stream the hidden output); B200MOE_L2_HINTS="h1,h2" overrides
+        env = os.getenv("B200MOE_L2_HINTS")
+        self.l2_hints = tuple(int(v) for v in env.split(",")) if env else (0, 0)
+        self.group_m = (0, 0)           # M-tiles per L2 chunk of the two GEMM kernels (0: automatic)
         self.drop_signal = False        # fault-injection aid for the timeout test
         self.profile = False            # record CUDA events between the phases of forward()
         self.phase_events = []
@@ -433,9 +438,10 @@ class MoELayer(nn.Module):
         ca.peer_arrived = heap.peer_ptrs(self.arrived)
 
         ga = nv.GemmArgs()
-        ga.num_groups, ga.K, ga.group_m = EL, D, 0
+        ga.num_groups, ga.K, ga.group_m = EL, D, self.group_m[0]
         ga.status, ga.wait_budget_ns = status_p, self._budget_ns
         ga.cta_pair = self._cta_pair
+        ga.l2_hints = self.l2_hints[0]
         recv = self.recv[0]
         if cfg.gated:
             F = cfg.ffn_dim
@@ -447,10 +453,11 @@ class MoELayer(nn.Module):
             ev("dispatch+gemm1")
             # 4. GEMM2 + combine (one kernel)
             gb = nv.GemmArgs()
-            gb.num_groups, gb.N, gb.K, gb.n_out, gb.group_m = EL, D, F, D, 0
+            gb.num_groups, gb.N, gb.K, gb.n_out, gb.group_m = EL, D, F, D, self.group_m[1]
             gb.group_rows = self.group_rows.data_ptr()
             gb.status, gb.wait_budget_ns = status_p, self._budget_ns
             gb.cta_pair = self._cta_pair
+            gb.l2_hints = self.l2_hints[1]
             nv.check(lib.b200_grouped_gemm(ptr(self.hidden), self.cap_rows, ptr(self.w2), nv.EPI_COMBINE,
                                            0, C.byref(gb), None, C.byref(ca), None, self._ctas, st),
                      "GEMM2+combine launch")

@@ -36,3 +36,10 @@ class HealthMonitor:
             self.last_error = f"{type(exc).__name__}: {exc}"[:300]
             return False
         return bool(vote.item() == 1)
+
+    def step_done(self) -> bool:
+        """Call after the step's ``torch.cuda.synchronize()``: a host-side handshake meaning "this
+        step is finished on every rank's device".  Once it returns True no rank has a store into
+        a peer's memory outstanding (the last kernel of a fused step publishes its retire stamp
+        into the peers' heaps), so a rank may leave now.  False when a peer did not answer."""
+        return self.all_alive(True)

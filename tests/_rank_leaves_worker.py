@@ -40,6 +40,10 @@ def main() -> None:
         torch.cuda.synchronize()
         layer.check_status()
         steps_done += 1
+        # "step done on the device" on every rank, agreed on the host: after this handshake no
+        # rank has a store into a peer's memory outstanding (the last kernel of a step publishes
+        # its retire stamp into the peers' heaps)
+        monitor.step_done()
         if rank == 1 and step == 1:
             print("rank1: leaving between steps", flush=True)
             sys.stdout.flush()

@@ -275,6 +275,7 @@ def test_padded_all_to_all_engine_repeats_without_memsets(dev, e_local, H, T, k,
         off = 0
         for e, n in enumerate(counts.reshape(-1).tolist()):
             assert torch.equal(out[e, 0, :n], payload[off:off + n]), e
+            assert float((out[e, 0, n:].float() - 7.0).abs().sum()) == 0.0      # padding rows untouched
             off += n
         if combine:
             a2a.send_back()
