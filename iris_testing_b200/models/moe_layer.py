@@ -140,6 +140,7 @@ class MoELayer(nn.Module):
         env = os.getenv("B200MOE_L2_HINTS")
         self.l2_hints = tuple(int(v) for v in env.split(",")) if env else (0, 0)
         self.group_m = (0, 0)           # M-tiles per L2 chunk of the two GEMM kernels (0: automatic)
+        self.tma_store = os.getenv("B200MOE_TMA_STORE", "1") != "0"   # hidden output through bulk tensor stores
         self.drop_signal = False        # fault-injection aid for the timeout test
         self.profile = False            # record CUDA events between the phases of forward()
         self.phase_events = []
@@ -442,6 +443,7 @@ class MoELayer(nn.Module):
         ga.status, ga.wait_budget_ns = status_p, self._budget_ns
         ga.cta_pair = self._cta_pair
         ga.l2_hints = self.l2_hints[0]
+        ga.tma_store = 0 if self.tma_store else -1
         recv = self.recv[0]
         if cfg.gated:
             F = cfg.ffn_dim
