@@ -503,13 +503,16 @@ class MoELayer(nn.Module):
         points are resolved outside the capture."""
         T = self.max_tokens if num_tokens is None else int(num_tokens)
         dev = self.heap.device
-        self._graph_x = torch.zeros((T, self.cfg.hidden_dim), dtype=self.cfg.dtype, device=dev)
+        # the warm-up input is random, not zero: equal logits would send every token of every rank
+        # to the first experts and overflow a capacity sized for balanced routing
+        self._graph_x = torch.randn((T, self.cfg.hidden_dim), device=dev).to(self.cfg.dtype)
         side = torch.cuda.Stream(dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             self._forward_fused(self._graph_x)          # warm-up outside the capture
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
+        self.check_status()
         self._graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self._graph):
             self._graph_y = self._forward_fused(self._graph_x)

@@ -107,6 +107,12 @@ def test_heap_backends(world: int, rank: int, dev) -> None:
     reads back what the others wrote, on both heap back-ends; closing the heaps gives the
     memory back."""
     from iris_testing_b200.parallel.symm import SymmetricHeap
+    # the first use of the communicator and of peer access allocates driver / NCCL memory of its own:
+    # warm both back-ends up before the reference reading
+    dist.all_reduce(torch.zeros(1, device=dev))
+    for backend in ("vmm", "ipc"):
+        SymmetricHeap(8 << 20, backend=backend).close()
+        dist.barrier()
     torch.cuda.synchronize()
     free0, _ = torch.cuda.mem_get_info()
     for backend in ("vmm", "ipc"):
