@@ -38,8 +38,9 @@ import torch.distributed as dist
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-from iris_testing_b200.bench_harness import (MODEL_DEFAULTS, ClockSampler, describe_config,  # noqa: E402
-                                             device_timed, e2e_loop, fence, make_config, max_over_ranks)
+from iris_testing_b200.bench_harness import (MODEL_DEFAULTS, ClockSampler, NvlinkCounters,  # noqa: E402
+                                             describe_config, device_timed, e2e_loop, fence, make_config,
+                                             max_over_ranks)
 
 METRIC = "moe_a2a_gemm_layer_us_max_over_ranks"
 METRIC_A2A = "padded_a2a_us_max_over_ranks"
@@ -83,8 +84,12 @@ def run_arm(args, arm, cfg, rank, world, local, dev, impl, count_fn=None) -> int
         arm.run(arm.inputs[i & 1], i)
     fence(world)
     arm.check_status()
+    links = NvlinkCounters(local)
     before = count_fn() if count_fn else 0
+    nv0 = links.read()
     us = device_timed(arm, args.steps, world, sampler)
+    nv1 = links.read()
+    algo = arm.remote_bytes()          # from the routing of the last timed step
     launches = int(count_fn() - before) if count_fn else 0
     clocks = sampler.stop()
     arm.check_status()
@@ -99,9 +104,57 @@ def run_arm(args, arm, cfg, rank, world, local, dev, impl, count_fn=None) -> int
     if count_fn and launches != arm.launches_expected(args.steps):      # counted vs expected: report only
         print(f"note: {launches} launches counted, {arm.launches_expected(args.steps)} expected",
               file=sys.stderr, flush=True)
-    emit(args, cfg, rank, world, us, e2e, launches, clocks, impl, arm.timed, arm.memory(), check,
-         extra=getattr(arm, "extra", None))
+    extra = dict(getattr(arm, "extra", None) or {})
+    # NVLink bytes of rank 0's GPU during the device-timed region (NVML counters, read only) next
+    # to the bytes the routing says must cross the links
+    if nv0 is not None and nv1 is not None:
+        extra["nvlink"] = dict(tx_bytes_per_step=round((nv1[0] - nv0[0]) / args.steps),
+                               rx_bytes_per_step=round((nv1[1] - nv0[1]) / args.steps),
+                               algorithmic_bytes_per_step=algo, source="NVML NVLINK_THROUGHPUT_DATA_TX/RX, rank 0")
+    elif algo is not None:
+        extra["nvlink"] = dict(counters="not readable on this box", algorithmic_bytes_per_step=algo)
+    emit(args, cfg, rank, world, us, e2e, launches, clocks, impl, arm.timed, arm.memory(), check, extra=extra)
     return 0 if (check is None or check.get("ok", True)) else 3
+
+
+SWEEPS = {
+    # padded all-to-all alone, dispatch and dispatch+combine: batch sweep at S=1024, sequence sweep at B=4
+    "config2": [dict(mode="a2a", batch=b, seq=1024, combine=c) for c in (False, True) for b in (1, 2, 4, 8, 16)]
+               + [dict(mode="a2a", batch=4, seq=q, combine=c) for c in (False, True)
+                  for q in (128, 256, 512, 2048, 4096)],
+    # fine-grained experts: experts over the whole group x top-k
+    "config4": [dict(mode="layer", model="fine-grained", experts=e, topk=k, batch=8, seq=2048)
+                for e in (8, 32, 128) for k in (1, 2, 8)]
+               + [dict(mode="layer", model="fine-grained", experts=e, topk=k, batch=8, seq=2048)
+                  for e, k in ((16, 2), (64, 2), (64, 4), (64, 8))],
+    # large experts, skewed and balanced routing
+    "config5": [dict(mode="layer", model="large", zipf=z, batch=8, seq=4096, experts=0, topk=0) for z in (1.2, 0.0)],
+}
+
+
+def run_points(args, make_arm, rank, world, local, dev, impl, count_fn=None) -> int:
+    """One JSON line per point of ``--sweep`` (or the single configuration), in one process."""
+    import copy
+    import gc
+    points = SWEEPS[args.sweep] if args.sweep else [dict()]
+    rc = 0
+    for pt in points:
+        a = copy.copy(args)
+        for k, v in pt.items():
+            setattr(a, k, v)
+        if a.mode == "layer" and a.experts and a.experts % world:
+            continue                                    # this expert count cannot be split over the ranks
+        if a.mode == "layer" and a.experts and a.topk > a.experts:
+            continue
+        cfg = make_config(a, world)
+        arm = make_arm(a)
+        rc = max(rc, run_arm(a, arm, cfg, rank, world, local, dev, impl, count_fn))
+        arm.close()
+        del arm
+        gc.collect()
+        torch.cuda.empty_cache()
+        fence(world)
+    return rc
 
 
 def run_ours(args) -> int:
@@ -110,11 +163,10 @@ def run_ours(args) -> int:
     rank, world, local, dev = init_dist(args.gpus)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    cfg = make_config(args, world)
-    arm = (LayerArm if args.mode == "layer" else A2AArm)(args, rank, world, dev)
     count_fn = _native.lib().b200_launch_count      # incremented by every native launcher
     count_fn.restype = ctypes.c_longlong
-    rc = run_arm(args, arm, cfg, rank, world, local, dev, "ours", count_fn)
+    rc = run_points(args, lambda a: (LayerArm if a.mode == "layer" else A2AArm)(a, rank, world, dev),
+                    rank, world, local, dev, "ours", count_fn)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -164,10 +216,12 @@ def run_reference(args) -> int:
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29577")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
-    cfg = make_config(args, world)
-    arm = (RefLayerArm if args.mode == "layer" else RefA2AArm)(ref_baseline, ref_utils, args, rank, world, dev)
-    arm.extra = {"ref_packer": arm.packer}
-    rc = run_arm(args, arm, cfg, rank, world, local, dev, "reference")
+    def make(a):
+        arm = (RefLayerArm if a.mode == "layer" else RefA2AArm)(ref_baseline, ref_utils, a, rank, world, dev)
+        arm.extra = {"ref_packer": arm.packer}
+        return arm
+
+    rc = run_points(args, make, rank, world, local, dev, "reference")
     dist.barrier()
     dist.destroy_process_group()
     return rc
@@ -192,6 +246,8 @@ def main() -> None:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--check-tokens", type=int, default=2048)
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--sweep", choices=sorted(SWEEPS), default=None,
+                    help="run every point of a published sweep in this one process, one JSON line each")
     ap.add_argument("--ref-packer", choices=["auto", "reference", "vectorized"], default="auto",
                     help="reference arm: its own Python packer, or the same payload built with tensor ops "
                          "(auto: its own packer up to 65536 routed copies)")

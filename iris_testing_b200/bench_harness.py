@@ -125,6 +125,48 @@ class ClockSampler:
         return out
 
 
+# --------------------------------------------------------------------------- NVLink counters
+class NvlinkCounters:
+    """Reads the GPU's NVLink data-byte counters through NVML (queries only, nothing is set or
+    reset).  ``read()`` returns (tx_bytes, rx_bytes) summed over all links, or None where the
+    driver does not expose the counters."""
+
+    def __init__(self, gpu_index: int) -> None:
+        self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            # NVML enumerates physical GPUs; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = gpu_index
+            if vis:
+                ids = [v.strip() for v in vis.split(",") if v.strip()]
+                if gpu_index < len(ids) and ids[gpu_index].isdigit():
+                    phys = int(ids[gpu_index])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+        except Exception:
+            self.handle = None
+
+    def read(self):
+        if self.handle is None:
+            return None
+        nv = self.nv
+        try:
+            all_links = 0xFFFFFFFF
+            vals = nv.nvmlDeviceGetFieldValues(self.handle, [
+                (nv.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX, all_links),
+                (nv.NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_RX, all_links)])
+            out = []
+            for v in vals:
+                if v.nvmlReturn != 0:
+                    return None
+                out.append(int(v.value.ullVal) * 1024)      # the counters are in KiB
+            return tuple(out)
+        except Exception:
+            return None
+
+
 # --------------------------------------------------------------------------- loops
 def fence(world: int) -> None:
     if world > 1:
@@ -290,6 +332,19 @@ class LayerArm:
     def launches_expected(self, steps: int) -> int:
         return self.layer.launches_per_forward * steps
 
+    def remote_bytes(self) -> Optional[dict]:
+        """Algorithmic bytes per step that must cross NVLink on this rank: rows routed to other
+        ranks (dispatch, out) and, for the combine, their results coming back (in)."""
+        cfg = self.cfg
+        idx, _ = self.layer.last_routing
+        dst = (idx.reshape(-1) // cfg.e_local)
+        remote_rows = int((dst != self.rank).sum().item())
+        return dict(dispatch_tx=remote_rows * cfg.hidden_dim * 2, combine_rx=remote_rows * cfg.out_dim * 2)
+
+    def close(self) -> None:
+        self.layer = None
+        self.heap.close()
+
     def check(self, tokens: int = 2048) -> dict:
         """One step of at most ``tokens`` tokens per rank against the dense single-process oracle
         over the all-gathered expert weights (the correctness report of the reference's
@@ -391,6 +446,18 @@ class A2AArm:
     def launches_expected(self, steps: int) -> int:
         return (4 if self.args.combine else 2) * steps
 
+    def remote_bytes(self) -> Optional[dict]:
+        c = self.routed[0]["counts"]
+        remote_rows = int(c.sum().item()) - int(c[self.rank].sum().item())
+        out = dict(dispatch_tx=remote_rows * self.H * 2)
+        if self.args.combine:
+            out["combine_rx"] = remote_rows * self.H * 2
+        return out
+
+    def close(self) -> None:
+        self.a2a = None
+        self.heap.close()
+
     def check(self, tokens: int = 0) -> dict:
         """The reference's correctness report (benchmark.py:354-440): pca exact, valid region of
         token_buf bit-equal to the library all-to-all re-laid out, and with ``--combine`` the
@@ -462,6 +529,12 @@ class _RefBase:
 
     def launches_expected(self, steps: int) -> int:
         return 0
+
+    def remote_bytes(self):
+        return None
+
+    def close(self) -> None:
+        self.prepared = None
 
     def _prepare(self, x, router, k, E, bias, H):
         """Routing, packing and receive-side bookkeeping of one input (untimed, as in the
