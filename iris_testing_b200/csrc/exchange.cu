@@ -155,11 +155,12 @@ struct PaddedArgs {
   int rank, world, e_local, cap, block_m;
   long long row_bytes;
   int mirror;
+  int plain;       // 1: rows move as 16-byte loads/stores of all threads of a block instead of bulk copies
   int* status;
   unsigned long long budget_ns;
 };
 
-__global__ void __launch_bounds__(A2A_WARPS * 32)
+__global__ void __launch_bounds__(256)
 padded_bulk_kernel(const uint8_t* __restrict__ src_rows, const int* __restrict__ counts,
                    const int* __restrict__ dst_offsets, PaddedArgs a) {
   extern __shared__ __align__(128) uint8_t a2a_smem[];
@@ -169,7 +170,7 @@ padded_bulk_kernel(const uint8_t* __restrict__ src_rows, const int* __restrict__
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int W = a.world, EL = a.e_local;
   if (tid == 0) s_abort = 0;
-  if (lane == 0) {
+  if (lane == 0 && warp < A2A_WARPS) {
     mbar_init(&bars[warp][0], 1);
     mbar_init(&bars[warp][1], 1);
     fence_mbar_init();
@@ -214,13 +215,61 @@ padded_bulk_kernel(const uint8_t* __restrict__ src_rows, const int* __restrict__
     }
   }
 
+  const int tpc = (a.cap + a.block_m - 1) / a.block_m;
+  const long long total = static_cast<long long>(W) * EL * tpc;
+  if (a.plain) {
+    // ---- tiles: one block per unit, every warp copies rows with eight 16-byte accesses in
+    // flight per lane; several blocks per SM hide each other's end-of-tile fence
+    __shared__ unsigned s_entered;
+    if (tid == 0) s_entered = a.mirror ? 0xffffffffu : 0u;
+    __syncthreads();
+    const int nwarps = blockDim.x >> 5;
+    const int row16 = static_cast<int>(a.row_bytes / 16);
+    for (long long u = blockIdx.x; u < total; u += gridDim.x) {
+      const int d = static_cast<int>(u % W);
+      const long long rest = u / W;
+      const int e = static_cast<int>(rest % EL), mt = static_cast<int>(rest / EL);
+      const int peer = (a.rank + d) % W;
+      const int n_true = a.mirror ? __ldcg(counts + e * W + peer) : counts[peer * EL + e];
+      if (n_true > a.cap && mt == 0 && tid == 0) report_status(a.status, ST_OVERFLOW);
+      const int n = min(n_true, a.cap);
+      const int m0 = mt * a.block_m;
+      if (m0 >= n) continue;
+      const int rows = min(a.block_m, n - m0);
+      if (!(s_entered >> peer & 1u)) {          // uniform: s_entered only changes between barriers
+        if (tid == 0 && wait_flag_geq(a.entered_local + peer, a.epoch, w, ST_TIMEOUT_BARRIER))
+          s_entered |= 1u << peer;
+        __syncthreads();
+        if (s_abort) break;
+      }
+      const uint8_t* src;
+      uint8_t* dst;
+      if (!a.mirror) {
+        src = src_rows + (static_cast<long long>(s_eoff[peer * EL + e]) + m0) * a.row_bytes;
+        dst = reinterpret_cast<uint8_t*>(a.token_buf.p[peer]) +
+              ((static_cast<long long>(e) * W + a.rank) * a.cap + m0) * a.row_bytes;
+      } else {
+        src = src_rows + ((static_cast<long long>(e) * W + peer) * a.cap + m0) * a.row_bytes;
+        dst = reinterpret_cast<uint8_t*>(a.token_buf.p[peer]) +
+              ((static_cast<long long>(a.rank) * EL + e) * a.cap + m0) * a.row_bytes;
+      }
+      for (int r = warp; r < rows; r += nwarps)
+        copy_row_16(reinterpret_cast<uint4*>(dst + r * a.row_bytes),
+                    reinterpret_cast<const uint4*>(src + r * a.row_bytes), row16, lane);
+      __syncthreads();
+      if (tid == 0) {
+        fence_acq_rel_sys();
+        red_add_release_sys(reinterpret_cast<uint32_t*>(a.token_sync.p[peer]) + (a.mirror ? a.rank : e), 1u);
+      }
+    }
+    return;
+  }
+
   // ---- tiles: one worker warp per unit, lane 0 drives the bulk copies
-  if (lane != 0) return;
+  if (lane != 0 || warp >= A2A_WARPS) return;
   uint8_t* buf[2] = {a2a_smem + (warp * 2) * A2A_CHUNK, a2a_smem + (warp * 2 + 1) * A2A_CHUNK};
   uint32_t phase[2] = {0u, 0u};
   unsigned entered_ok = a.mirror ? 0xffffffffu : 0u;
-  const int tpc = (a.cap + a.block_m - 1) / a.block_m;
-  const long long total = static_cast<long long>(W) * EL * tpc;
   const long long worker = static_cast<long long>(blockIdx.x) * A2A_WARPS + warp;
   const long long nworkers = static_cast<long long>(gridDim.x) * A2A_WARPS;
   for (long long u = worker; u < total; u += nworkers) {
@@ -634,7 +683,7 @@ int b200_padded_exchange(const void* rows, const int* counts, const int* dst_off
                          const unsigned long long* peer_token_sync,
                          const unsigned long long* peer_entered, const void* entered_local,
                          unsigned int epoch, int rank, int world, int e_local, int cap, int hidden_dim,
-                         int elem_bytes, int block_m, int mirror, int num_blocks, int* status,
+                         int elem_bytes, int block_m, int mirror, int num_blocks, int plain, int* status,
                          unsigned long long budget_ns, void* stream) {
   if (world < 1 || world > B200_MAX_WORLD || world * e_local > B200_MAX_EXPERTS || block_m < 1 || cap < 1 ||
       (static_cast<long long>(hidden_dim) * elem_bytes) % 16 != 0 || num_blocks < 1 ||
@@ -661,10 +710,15 @@ int b200_padded_exchange(const void* rows, const int* counts, const int* dst_off
   a.rank = rank; a.world = world; a.e_local = e_local; a.cap = cap; a.block_m = block_m;
   a.row_bytes = static_cast<long long>(hidden_dim) * elem_bytes;
   a.mirror = mirror;
+  a.plain = plain ? 1 : 0;
   a.status = status;
   a.budget_ns = budget_ns;
-  b200::padded_bulk_kernel<<<num_blocks, b200::A2A_WARPS * 32, smem, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint8_t*>(rows), counts, dst_offsets, a);
+  if (plain)
+    b200::padded_bulk_kernel<<<num_blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(rows), counts, dst_offsets, a);
+  else
+    b200::padded_bulk_kernel<<<num_blocks, b200::A2A_WARPS * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(rows), counts, dst_offsets, a);
   b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

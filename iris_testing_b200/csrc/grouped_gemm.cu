@@ -422,6 +422,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&c.empty[stage], phase ^ 1u, w, ST_TIMEOUT_PIPE_EMPTY)) { ok = false; break; }
           uint8_t* sa = stage_base + stage * STAGE_BYTES;
+          if (ga.l2_hints & 8) {
+            // measurement aid (results are wrong): only every fourth k-block is fetched, the others
+            // reuse whatever the stage holds -- shows what the operand traffic costs
+            if ((kb & 3) != 0) {
+              if (cta_rank == 0) mbar_arrive(&c.full[stage]);
+              ++issued;
+              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+              continue;
+            }
+          }
           if constexpr (CG == 2) {
             // the pair leader's barrier collects the bytes of both CTAs' loads
             if (cta_rank == 0) mbar_expect_tx(&c.full[stage], STAGE_BYTES * 2);

@@ -36,7 +36,7 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
                  epilogue: int = nv.EPI_STORE, out: Optional[torch.Tensor] = None,
                  status: Optional[torch.Tensor] = None, group_m: int = 0,
                  num_ctas: Optional[int] = None, wait_budget_ms: float = 2000.0,
-                 cta_pair: Optional[bool] = None) -> torch.Tensor:
+                 cta_pair: Optional[bool] = None, l2_hints: int = 0) -> torch.Tensor:
     """out[rows of group g] = a[rows of group g] @ w_kmajor[g].T   (bf16 in, fp32 accumulate).
 
     a          [M, K] bf16, groups packed back to back
@@ -90,6 +90,7 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     if cta_pair is None:
         cta_pair = M >= 256 * G
     ga.cta_pair = int(bool(cta_pair))
+    ga.l2_hints = int(l2_hints)
     ctas = num_ctas or sm_count(a.device)
     rc = nv.lib().b200_grouped_gemm(ptr(a), M, ptr(w_kmajor), epilogue, 0, C.byref(ga), None, None,
                                     None, ctas, stream_ptr(a))

@@ -16,6 +16,7 @@ completion is a local device-side wait on the flags.  Rows travel as bulk copies
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -33,7 +34,7 @@ def _exchange_fn():
     u64p = C.POINTER(C.c_ulonglong)
     return declare("b200_padded_exchange",
                    [C.c_void_p, C.c_void_p, C.c_void_p, u64p, u64p, u64p, u64p, u64p, C.c_void_p, C.c_uint,
-                    C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                    C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                     C.c_void_p, C.c_ulonglong, C.c_void_p])
 
 
@@ -47,7 +48,7 @@ class PaddedAllToAll:
 
     def __init__(self, heap, e_local: int, capacity: int, hidden_dim: int, dtype: torch.dtype,
                  with_return: bool = False, num_blocks: Optional[int] = None,
-                 wait_budget_ms: float = 2000.0) -> None:
+                 wait_budget_ms: float = 2000.0, copy_mode: Optional[str] = None) -> None:
         self.heap, self.world, self.rank = heap, heap.world, heap.rank
         self.e_local, self.cap, self.H, self.dtype = int(e_local), int(capacity), int(hidden_dim), dtype
         self.esz = torch.empty((), dtype=dtype).element_size()
@@ -65,7 +66,13 @@ class PaddedAllToAll:
                                      ret_sync=heap.zeros((W,), i32))
             self._ticket = torch.zeros(1, dtype=i32, device=heap.device)
         self.epoch = 0
-        self.blocks = int(num_blocks) if num_blocks else sm_count(heap.device)
+        # "stores": every thread moves 16-byte pieces (several blocks per SM); "bulk": one lane per warp
+        # drives bulk copies through shared memory (one block per SM)
+        self.copy_mode = (copy_mode or os.getenv("B200MOE_A2A_COPY", "stores")).lower()
+        require(self.copy_mode in ("stores", "bulk"), "copy_mode must be 'stores' or 'bulk'")
+        self._plain = int(self.copy_mode == "stores")
+        per_sm = 4 if self._plain else 1
+        self.blocks = int(num_blocks) if num_blocks else sm_count(heap.device) * per_sm
         self.budget_ns = int(wait_budget_ms * 1e6)
         torch.cuda.synchronize(heap.device)
         if W > 1:
@@ -94,7 +101,7 @@ class PaddedAllToAll:
         rc = _exchange_fn()(ptr(payload), ptr(send_counts), ptr(dst_offsets), h.peer_ptrs(b.pca),
                             h.peer_ptrs(b.token_buf), h.peer_ptrs(b.counts_ready), h.peer_ptrs(b.token_sync),
                             h.peer_ptrs(self.entered), ptr(self.entered), self.epoch, self.rank, self.world,
-                            self.e_local, self.cap, self.H, self.esz, tile_rows(), 0, self.blocks,
+                            self.e_local, self.cap, self.H, self.esz, tile_rows(), 0, self.blocks, self._plain,
                             ptr(h.status), self.budget_ns, stream_ptr(payload))
         nv.check(rc, "padded dispatch launch")
         return b.token_buf
@@ -118,7 +125,7 @@ class PaddedAllToAll:
         require(src.is_contiguous() and tuple(src.shape) == tuple(b.token_buf.shape), "out_buf has the wrong shape")
         rc = _exchange_fn()(ptr(src), ptr(b.pca), None, None, h.peer_ptrs(r.ret_buf), None,
                             h.peer_ptrs(r.ret_sync), None, None, self.epoch, self.rank, self.world,
-                            self.e_local, self.cap, self.H, self.esz, tile_rows(), 1, self.blocks,
+                            self.e_local, self.cap, self.H, self.esz, tile_rows(), 1, self.blocks, self._plain,
                             ptr(h.status), self.budget_ns, stream_ptr(src))
         nv.check(rc, "padded return launch")
         return r.ret_buf

@@ -243,9 +243,10 @@ def test_device_row_counts_beyond_the_buffers_are_reported_not_stored(dev):
     assert packed.shape[0] == 8 and st2.tolist()[:2] == [10, 11]
 
 
+@pytest.mark.parametrize("mode", ["stores", "bulk"])
 @pytest.mark.parametrize("e_local,H,T,k,combine", [(2, 128, 100, 2, False), (8, 4096, 1024, 2, True),
                                                    (4, 768, 777, 4, True), (1, 264, 50, 1, True)])
-def test_padded_all_to_all_engine_repeats_without_memsets(dev, e_local, H, T, k, combine):
+def test_padded_all_to_all_engine_repeats_without_memsets(dev, e_local, H, T, k, combine, mode):
     """``PaddedAllToAll`` on a world of one, three exchanges in a row with changing routing: flags
     re-armed in-kernel, valid rows bit-equal to the payload, padding never written, and with
     the return path the weighted sum of the rows that come home."""
@@ -263,7 +264,7 @@ def test_padded_all_to_all_engine_repeats_without_memsets(dev, e_local, H, T, k,
         n = r[1].to(torch.int64)
         assert c == [int(n.max()), int(n.sum()), int(n.sum()), int(n.sum())]     # CAP, M, rows received
     cap = max(c[0] for c in caps)
-    a2a = PaddedAllToAll(heap, e_local, cap, H, torch.bfloat16, with_return=combine)
+    a2a = PaddedAllToAll(heap, e_local, cap, H, torch.bfloat16, with_return=combine, copy_mode=mode)
     a2a.token_buf.fill_(7.0)                                  # rows no exchange has used stay as they were
     high = torch.zeros(e_local, dtype=torch.int64)            # most rows each cell has ever held
     for x, (payload, counts, dst_off, _, idx, wgt, plan) in zip(xs, routed):

@@ -147,7 +147,7 @@ def test_heap_backends(world: int, rank: int, dev) -> None:
     assert abs(free1 - free0) <= (16 << 20), (free0, free1)
 
 
-def test_padded_engine(heap, e_local: int, H: int, T: int, topk: int) -> None:
+def test_padded_engine(heap, e_local: int, H: int, T: int, topk: int, copy_mode: str) -> None:
     """The epoch-driven padded exchange with router-driven ragged counts, several exchanges in a
     row with changing routing: device-side capacity rule against host reductions, pca and
     the valid rows of token_buf bit-equal to the library all-to-all re-laid out, and the rows
@@ -169,7 +169,7 @@ def test_padded_engine(heap, e_local: int, H: int, T: int, topk: int) -> None:
                 int(allc[:, rank].sum())]
         assert c == want, (rank, c, want)
     cap = max(c[0] for c in caps)
-    a2a = PaddedAllToAll(heap, e_local, cap, H, torch.bfloat16, with_return=True)
+    a2a = PaddedAllToAll(heap, e_local, cap, H, torch.bfloat16, with_return=True, copy_mode=copy_mode)
     for x, (payload, counts, dst_off, _, idx, wgt, plan) in zip(xs, routed):
         a2a.dispatch(payload, counts, dst_off)
         a2a.wait()
@@ -249,8 +249,9 @@ def _worker(rank: int, world: int) -> None:
     say("test_custom_a2a(e_local=2, H=128, cap=32) PASSED")
     test_custom_a2a(heap, e_local=4, hidden_dim=256, cap=16)
     say("test_custom_a2a(e_local=4, H=256, cap=16) PASSED")
-    test_padded_engine(heap, e_local=4, H=512, T=600, topk=2)
-    say("test_padded_engine PASSED")
+    for mode in ("stores", "bulk"):
+        test_padded_engine(heap, e_local=4, H=512, T=600, topk=2, copy_mode=mode)
+        say(f"test_padded_engine({mode}) PASSED")
     test_fused_layer(heap, D=256, F=512, e_local=2, topk=2, T=300)
     say("test_fused_layer(gated) PASSED")
     test_fused_layer(heap, D=256, F=0, e_local=4, topk=1, T=77)
