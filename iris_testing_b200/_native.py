@@ -106,6 +106,8 @@ class GemmArgs(C.Structure):
         ("a_rows", C.c_longlong),
         ("l2_hints", C.c_int),
         ("tma_store", C.c_int),
+        ("wide_tiles", C.c_int),
+        ("dbg", C.c_void_p),
     ]
 
 

@@ -85,15 +85,27 @@ struct __align__(16) ControlSmem {
 };
 
 // Per-variant geometry.  CG = CTAs cooperating on one MMA (tcgen05 cta_group): with CG == 2
-// the pair computes a 256 x 256 tile, each CTA staging its own 128 rows of A and its own
-// 128 of the 256 weight rows, so a stage is 32 KiB per CTA and six stages fit.
-template <int CG>
+// the pair computes a 256-row tile, each CTA staging its own 128 rows of A and its own
+// 128 of every 256 weight rows.  NT = 256-column accumulators that make up one tile:
+//  * NT == 1: a 256-column tile; the two TMEM accumulators double-buffer (the epilogue of
+//    tile i overlaps the MMAs of tile i+1); a stage is 32 KiB per CTA of a pair, six fit.
+//  * NT == 2 (pairs only): a 512-column tile that uses BOTH accumulators at once, so one
+//    stage of activations feeds twice the math: 25 % fewer operand bytes come out of L2
+//    per FLOP, which under the power cap is worth more clock than the lost double
+//    buffering costs (measured on B200: with three quarters of the operand loads skipped
+//    the same kernel holds 1350 MHz instead of 1035 MHz).  The epilogue is hidden
+//    by letting the second half's MMAs of the next tile trail the first half's by up to
+//    STAGES-1 k-blocks.  A stage is 48 KiB per CTA, four fit.
+template <int CG, int NT = 1>
 struct Geo {
-  static constexpr int STAGES = CG == 2 ? 6 : 4;
-  static constexpr int B_ROWS = BN / CG;
-  static constexpr int B_STAGE_BYTES = B_ROWS * BK * 2;
+  static_assert(NT == 1 || CG == 2, "wide tiles are built from CTA pairs");
+  static constexpr int STAGES = NT == 2 ? 4 : (CG == 2 ? 6 : 4);
+  static constexpr int B_ROWS = BN / CG;                       // weight rows per CTA per accumulator
+  static constexpr int B_HALF_BYTES = B_ROWS * BK * 2;
+  static constexpr int B_STAGE_BYTES = NT * B_HALF_BYTES;
   static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
   static constexpr int TM = BM * CG;                   // rows of a scheduling tile
+  static constexpr int TILE_N = BN * NT;               // weight rows (accumulator columns) of a tile
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STG_BYTES + (int)sizeof(ControlSmem) + 1024;
   static_assert(SMEM_BYTES <= 232448, "exceeds 227 KiB of shared memory per CTA");
 };
@@ -219,7 +231,7 @@ __device__ __forceinline__ void build_dispatch_tables(ControlSmem& c, const b200
   }
 }
 
-template <int EPI, bool FUSED, int CG>
+template <int EPI, bool FUSED, int CG, int NT>
 __global__ void __launch_bounds__(FUSED ? NUM_THREADS_FUSED : NUM_THREADS_PLAIN, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
                     const __grid_constant__ CUtensorMap tmap_a1,
@@ -257,7 +269,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  using S = Geo<CG>;
+  using S = Geo<CG, NT>;
   constexpr int STAGES = S::STAGES;
   constexpr int STAGE_BYTES = S::STAGE_BYTES;
   uint8_t* stage_base = smem;
@@ -269,7 +281,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
   const int lane = tid & 31;
   const int nthreads = blockDim.x;
   const int G = FUSED ? da.e_local : ga.num_groups;
-  const int TN = (ga.N + BN - 1) / BN;
+  const int TN = (ga.N + S::TILE_N - 1) / S::TILE_N;
   const int KB = (ga.K + BK - 1) / BK;
   const int gm = ga.group_m > 0 ? ga.group_m : 16;
   // CTA pair bookkeeping: both CTAs of a pair walk the same tile list; CTA `cta_rank`
@@ -418,7 +430,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
               l2_prefetch_bulk(base + off, static_cast<uint32_t>(min(static_cast<size_t>(32768), total - off)));
           }
         }
-        const int brow = g * ga.N + n * BN + static_cast<int>(cta_rank) * S::B_ROWS;
+        // first weight row of accumulator 0 for this CTA; accumulator 1 (wide tiles) is BN rows on
+        const int brow = g * ga.N + n * S::TILE_N + static_cast<int>(cta_rank) * S::B_ROWS;
         for (int kb = 0; kb < KB; ++kb) {
           if (!mbar_wait(&c.empty[stage], phase ^ 1u, w, ST_TIMEOUT_PIPE_EMPTY)) { ok = false; break; }
           uint8_t* sa = stage_base + stage * STAGE_BYTES;
@@ -438,10 +451,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
             const uint32_t lead_bar = map_to_cta(&c.full[stage], 0);
             if (hinted) {
               tma_load_2d_pair_hint(sa, &tmap_a, lead_bar, kb * BK, row0, pol_a);
-              tma_load_2d_pair_hint(sa + A_STAGE_BYTES, &tmap_b, lead_bar, kb * BK, brow, pol_b);
+#pragma unroll
+              for (int h = 0; h < NT; ++h)
+                tma_load_2d_pair_hint(sa + A_STAGE_BYTES + h * S::B_HALF_BYTES, &tmap_b, lead_bar, kb * BK,
+                                      brow + h * BN, pol_b);
             } else {
               tma_load_2d_pair(sa, &tmap_a, lead_bar, kb * BK, row0);
-              tma_load_2d_pair(sa + A_STAGE_BYTES, &tmap_b, lead_bar, kb * BK, brow);
+#pragma unroll
+              for (int h = 0; h < NT; ++h)
+                tma_load_2d_pair(sa + A_STAGE_BYTES + h * S::B_HALF_BYTES, &tmap_b, lead_bar, kb * BK,
+                                 brow + h * BN);
             }
           } else if (hinted) {
             mbar_expect_tx(&c.full[stage], static_cast<uint32_t>(STAGE_BYTES));
@@ -484,6 +503,56 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
       int it = 0;
       bool ok = !c.abort_flag;
       for (int idx = sched_id; ok && idx < total_tiles; idx += sched_stride, ++it) {
+        if constexpr (NT == 2) {
+          // Wide tile: accumulator h takes weight rows [h*256, +256) of the tile.  Accumulator 0 must
+          // be free before the first MMA; accumulator 1's MMAs may trail by up to LAG k-blocks
+          // (their stages stay occupied meanwhile), which covers the time the epilogue of the
+          // previous tile still needs for its second half.
+          constexpr int LAG = STAGES - 1;
+          const uint32_t par = static_cast<uint32_t>(it & 1);
+          if (!mbar_wait(&c.tmem_empty[0], par ^ 1u, w, ST_TIMEOUT_TMEM_EMPTY)) break;
+          tc_fence_after_sync();
+          bool h1_free = false;
+          int deferred = 0, dstage = stage, dkb = 0;      // k-blocks whose accumulator-1 MMAs are pending
+          for (int kb = 0; kb < KB; ++kb) {
+            if (!mbar_wait(&c.full[stage], phase, w, ST_TIMEOUT_PIPE_FULL)) { ok = false; break; }
+            tc_fence_after_sync();
+            {
+              const uint32_t sa = smem_u32(stage_base + stage * STAGE_BYTES);
+              const uint64_t adesc = make_smem_desc_sw128(sa);
+              const uint64_t bdesc = make_smem_desc_sw128(sa + A_STAGE_BYTES);
+#pragma unroll
+              for (int k = 0; k < BK / UMMA_K; ++k)
+                umma_bf16_ss_pair(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            ++deferred;
+            if (!h1_free) {
+              if (deferred >= LAG || kb == KB - 1) {
+                if (!mbar_wait(&c.tmem_empty[1], par ^ 1u, w, ST_TIMEOUT_TMEM_EMPTY)) { ok = false; break; }
+                h1_free = true;
+              } else if (mbar_try_wait(&c.tmem_empty[1], par ^ 1u)) {
+                h1_free = true;
+              }
+              if (h1_free) tc_fence_after_sync();
+            }
+            if (h1_free) {
+              for (; deferred > 0; --deferred, ++dkb) {
+                const uint32_t sa = smem_u32(stage_base + dstage * STAGE_BYTES);
+                const uint64_t adesc = make_smem_desc_sw128(sa);
+                const uint64_t bdesc = make_smem_desc_sw128(sa + A_STAGE_BYTES + S::B_HALF_BYTES);
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k)
+                  umma_bf16_ss_pair(tmem_base + BN, adesc + 2 * k, bdesc + 2 * k, idesc, (dkb | k) != 0 ? 1u : 0u);
+                umma_commit_pair(&c.empty[dstage], 3);     // both accumulators have consumed the stage
+                if (++dstage == STAGES) dstage = 0;
+              }
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          umma_commit_pair(&c.tmem_full[0], 3);
+          continue;
+        }
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(&c.tmem_empty[acc], acc_phase ^ 1u, w, ST_TIMEOUT_TMEM_EMPTY)) break;
@@ -539,16 +608,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
     for (int idx = sched_id; idx < total_tiles; idx += sched_stride, ++it) {
       int g, m, n;
       if (!decode_tile(c, G, TN, gm, idx, cursor, g, m, n)) break;
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
+      // NT == 1: the two accumulators alternate from tile to tile; NT == 2: both belong to this tile
+      const int acc_first = NT == 2 ? 0 : (it & 1);
+      const uint32_t acc_phase = NT == 2 ? static_cast<uint32_t>(it & 1) : static_cast<uint32_t>((it >> 1) & 1);
       const int half0 = m * S::TM + static_cast<int>(cta_rank) * BM;
       const int rows_in_tile = min(BM, c.g_rows[g] - half0);      // may be <= 0 for the upper half
       const int row0 = c.g_row_start[g] + half0;
       bool valid = row_in_tile < rows_in_tile;
 
       // warp-uniform decision: the TMEM loads below need the whole warp
-      const bool got = mbar_wait(&c.tmem_full[acc], acc_phase, w, ST_TIMEOUT_TMEM_FULL);
+      const bool prof = ga.dbg != nullptr && blockIdx.x == 0 && warp == 2 && lane == 0;
+      const uint64_t t_w0 = prof ? globaltimer_ns() : 0ull;
+      const bool got = mbar_wait(&c.tmem_full[acc_first], acc_phase, w, ST_TIMEOUT_TMEM_FULL);
       if (!__all_sync(0xffffffffu, got)) break;
+      if (prof) atomicAdd(ga.dbg + 0, globaltimer_ns() - t_w0);
       tc_fence_after_sync();
       // Row metadata is read only now: in the fused-dispatch build it is written by the
       // sending rank together with the row, and the accumulator being complete implies
@@ -576,6 +649,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
                  static_cast<unsigned long long>(row0 + row_in_tile) * ga.ldo * 2ull;
       }
 
+#pragma unroll 1
+      for (int hh = 0; hh < NT; ++hh) {
+      const int acc = acc_first + hh;
+      const int n_sub = n * NT + hh;        // 256-column accumulator index along N
+      uint64_t t_p = prof ? globaltimer_ns() : 0ull;
+      uint64_t t_math = 0, t_store = 0;
       const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN;
 
       if constexpr (EPI == B200_EPI_ROUTER) {
@@ -670,13 +749,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
                 make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
           }
         }
+        if (prof) { const uint64_t t2 = globaltimer_ns(); t_math += t2 - t_p; t_p = t2; }
         if (p == PASSES - 1) {
           // every TMEM read of this accumulator is done: hand it back to the MMA warp
           tc_fence_before_sync();
           if constexpr (CG == 2) mbar_arrive_cluster(tmem_empty_addr[acc]);
           else mbar_arrive(&c.tmem_empty[acc]);
         }
-        const int box_col0 = n * OUT_TILE + p * STG_COLS;
+        const int box_col0 = n_sub * OUT_TILE + p * STG_COLS;
         if (EPI != B200_EPI_COMBINE && ga.tma_store && rows_in_tile >= (q + 1) * 32) {
           // all 32 rows of this warp are rows of the group: one bulk tensor store writes the box
           // (columns past the output width are clipped by the tensor map)
@@ -688,6 +768,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
             bulk_commit_group();
             store_pending = true;
           }
+          if (prof) { const uint64_t t2 = globaltimer_ns(); t_store += t2 - t_p; t_p = t2; }
           continue;
         }
         __syncwarp();
@@ -706,6 +787,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
           }
         }
         __syncwarp();
+        if (prof) { const uint64_t t2 = globaltimer_ns(); t_store += t2 - t_p; t_p = t2; }
+      }
+      if (prof) {
+        atomicAdd(ga.dbg + 1, t_math);
+        atomicAdd(ga.dbg + 2, t_store);
+        atomicAdd(ga.dbg + 3, 1ull);
       }
 
       if constexpr (EPI == B200_EPI_COMBINE) {
@@ -713,18 +800,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
         // so the counts are kept per destination rank (lane r of the warp keeps rank r's)
         // and published once, after this warp's last tile: a system-scope fence per tile
         // would stall the epilogue longer than a short-K tile takes to compute.
-        const unsigned grp = __match_any_sync(0xffffffffu, dst_rank);
-        const int leader_cnt = (dst_rank >= 0 && lane == (__ffs(grp) - 1)) ? __popc(grp) : 0;
+        const int cnt_rank = (n_sub * OUT_TILE < ga.n_out) ? dst_rank : -1;   // a half past the output width
+        const unsigned grp = __match_any_sync(0xffffffffu, cnt_rank);
+        const int leader_cnt = (cnt_rank >= 0 && lane == (__ffs(grp) - 1)) ? __popc(grp) : 0;
 #pragma unroll
         for (int r = 0; r < B200_MAX_WORLD; ++r) {
           // sum over the (at most one per group) leaders whose destination is rank r
-          const unsigned m = __ballot_sync(0xffffffffu, leader_cnt > 0 && dst_rank == r);
+          const unsigned m = __ballot_sync(0xffffffffu, leader_cnt > 0 && cnt_rank == r);
           if (m != 0u) {
             const int c2 = __shfl_sync(0xffffffffu, leader_cnt, __ffs(m) - 1);
             if (lane == r) pending_arrivals += c2;
           }
         }
       }
+      }   // accumulators of the tile
     }
     if (store_pending) bulk_wait_group<0>();   // shared memory stays allocated until the stores are done
     if constexpr (EPI == B200_EPI_COMBINE) {
@@ -861,15 +950,15 @@ static int make_tmap_bf16(CUtensorMap* tm, const void* base, long long rows, lon
 // Error code of launch_variant when not even one CTA (pair) of the variant can be resident.
 constexpr int ERR_NOT_RESIDENT = -18;
 
-template <int EPI, bool FUSED, int CG>
+template <int EPI, bool FUSED, int CG, int NT>
 static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta1, const CUtensorMap& tb,
                           const CUtensorMap& to, const b200_gemm_args& ga,
                           const b200_dispatch_args& da, const b200_combine_args& ca,
                           const b200_router_args& ra, int ctas, cudaStream_t stream) {
   static bool configured = false;
   static int resident_clusters = -1;
-  auto kern = grouped_gemm_kernel<EPI, FUSED, CG>;
-  constexpr int smem = Geo<CG>::SMEM_BYTES;
+  auto kern = grouped_gemm_kernel<EPI, FUSED, CG, NT>;
+  constexpr int smem = Geo<CG, NT>::SMEM_BYTES;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return static_cast<int>(e);
@@ -905,25 +994,25 @@ static int launch_variant(const CUtensorMap& ta, const CUtensorMap& ta1, const C
   return static_cast<int>(cudaLaunchKernelEx(&cfg, kern, ta, ta1, tb, to, ga, da, ca, ra));
 }
 
-template <int CG>
+template <int CG, int NT>
 static int launch_geometry(int epi, int fused, const CUtensorMap& ta, const CUtensorMap& ta1,
                            const CUtensorMap& tb, const CUtensorMap& to, const b200_gemm_args& ga,
                            const b200_dispatch_args& d, const b200_combine_args& c,
                            const b200_router_args& r, int ctas, cudaStream_t st) {
   if (!fused) {
     switch (epi) {
-      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, false, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
-      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, false, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
-      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, false, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, false, CG, NT>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, false, CG, NT>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, false, CG, NT>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
       case B200_EPI_ROUTER:
-        if constexpr (CG == 1) return launch_variant<B200_EPI_ROUTER, false, 1>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+        if constexpr (CG == 1) return launch_variant<B200_EPI_ROUTER, false, 1, 1>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
         break;
     }
   } else {
     switch (epi) {
-      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, true, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
-      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, true, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
-      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, true, CG>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_STORE: return launch_variant<B200_EPI_STORE, true, CG, NT>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_SILU_GATE: return launch_variant<B200_EPI_SILU_GATE, true, CG, NT>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
+      case B200_EPI_COMBINE: return launch_variant<B200_EPI_COMBINE, true, CG, NT>(ta, ta1, tb, to, ga, d, c, r, ctas, st);
     }
   }
   return -15;
@@ -1021,8 +1110,13 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
       ga_auto.group_m = static_cast<int>(gm < 1 ? 1 : (gm > 16 ? 16 : gm));
     }
     ga_auto.cta_pair = pair ? 1 : 0;
-    r = pair ? launch_geometry<2>(epi, fused, ta, ta1, tb, to, ga_auto, d, c, r2, num_ctas, st)
-             : launch_geometry<1>(epi, fused, ta, ta1, tb, to, ga_auto, d, c, r2, num_ctas, st);
+    // Wide (512-column) tiles: fewer operand bytes per FLOP, no accumulator double buffering.
+    // Only on request (wide_tiles > 0): measured on B200, the epilogue time they expose costs
+    // more than the saved operand traffic gains on the layer shapes of this library.
+    const bool wide = pair && ga->wide_tiles > 0 && ga->N >= 2 * BN;
+    r = !pair ? launch_geometry<1, 1>(epi, fused, ta, ta1, tb, to, ga_auto, d, c, r2, num_ctas, st)
+        : wide ? launch_geometry<2, 2>(epi, fused, ta, ta1, tb, to, ga_auto, d, c, r2, num_ctas, st)
+               : launch_geometry<2, 1>(epi, fused, ta, ta1, tb, to, ga_auto, d, c, r2, num_ctas, st);
     if (r == ERR_NOT_RESIDENT && pair) {   // no pair fits in this context: single-CTA tiles
       pair = false;
       continue;
@@ -1033,6 +1127,7 @@ int b200_grouped_gemm(const void* a, long long a_rows, const void* w, int epi, i
 }
 
 int b200_gemm_smem_bytes() { return b200::Geo<1>::SMEM_BYTES; }
+int b200_gemm_smem_bytes_wide() { return b200::Geo<2, 2>::SMEM_BYTES; }
 
 }  // extern "C"
 

@@ -88,6 +88,10 @@ typedef struct {
                                   // weights (evict first), 4 = stream the EPI 0/1 output; 0 = none
   int tma_store;                  // EPI 0/1: full 32-row boxes leave through bulk tensor stores (set by
                                   // the launcher when the output is 16-byte aligned; -1 on entry forbids it)
+  int wide_tiles;                 // CTA pairs: 1 = 512-column tiles (both accumulators per tile); 0 / -1 = off
+  unsigned long long* dbg;        // optional [8] profiling words of CTA 0's first epilogue warp: summed ns of
+                                  // [0] waiting for an accumulator, [1] reading TMEM + math + staging of
+                                  // one accumulator, [2] its stores, [3] accumulators processed
 } b200_gemm_args;
 
 // Router epilogue: the accumulator row holds the logits of one token.

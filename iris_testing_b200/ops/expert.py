@@ -36,7 +36,8 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
                  epilogue: int = nv.EPI_STORE, out: Optional[torch.Tensor] = None,
                  status: Optional[torch.Tensor] = None, group_m: int = 0,
                  num_ctas: Optional[int] = None, wait_budget_ms: float = 2000.0,
-                 cta_pair: Optional[bool] = None, l2_hints: int = 0) -> torch.Tensor:
+                 cta_pair: Optional[bool] = None, l2_hints: int = 0, wide_tiles: int = 0,
+                 epilogue_trace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[rows of group g] = a[rows of group g] @ w_kmajor[g].T   (bf16 in, fp32 accumulate).
 
     a          [M, K] bf16, groups packed back to back
@@ -45,6 +46,8 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     group_m    M-tiles per L2-blocking chunk; 0 picks about 48 MB of activations per chunk.
     cta_pair   True: two CTAs per MMA (tcgen05 cta_group::2, 256-row tiles); None picks it
                when the groups average at least 256 rows.
+    wide_tiles CTA pairs only: 512-column tiles that use both TMEM accumulators at once (25 % fewer
+               operand bytes per FLOP, but the epilogue is no longer hidden); 1 = on, 0 = off (default).
     epilogue   EPI_STORE -> out [M, N];  EPI_SILU_GATE -> out [M, N/2] where every
                256-row block of a group's weight holds 128 gate rows then 128 up rows.
     """
@@ -91,6 +94,8 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
         cta_pair = M >= 256 * G
     ga.cta_pair = int(bool(cta_pair))
     ga.l2_hints = int(l2_hints)
+    ga.wide_tiles = int(wide_tiles)
+    ga.dbg = None if epilogue_trace is None else epilogue_trace.data_ptr()   # int64 [8] profiling words
     ctas = num_ctas or sm_count(a.device)
     rc = nv.lib().b200_grouped_gemm(ptr(a), M, ptr(w_kmajor), epilogue, 0, C.byref(ga), None, None,
                                     None, ctas, stream_ptr(a))

@@ -70,7 +70,7 @@ def test_plan_and_pack(dev, T, k, E):
     assert torch.equal(pack_rows(x, p.send_order, k), cpu_ref.pack_ref(x, r.send_order, k))
 
 
-def _gemm_case(dev, rows_list, N, K, gated, pair=False):
+def _gemm_case(dev, rows_list, N, K, gated, pair=False, wide=0):
     from iris_testing_b200 import _native as nv
     from iris_testing_b200.ops import grouped_gemm
     G, M = len(rows_list), max(sum(rows_list), 1)
@@ -80,7 +80,7 @@ def _gemm_case(dev, rows_list, N, K, gated, pair=False):
     rows = torch.tensor(rows_list, dtype=torch.int32, device=dev)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     out = grouped_gemm(a, w, rows, epilogue=nv.EPI_SILU_GATE if gated else nv.EPI_STORE, status=status,
-                       cta_pair=pair)
+                       cta_pair=pair, wide_tiles=wide)
     ref = torch.zeros(M, N, device=dev)
     off = 0
     for gi, r in enumerate(rows_list):
@@ -106,6 +106,16 @@ def test_grouped_gemm_plain(dev, rows, N, K, pair):
 @pytest.mark.parametrize("pair", [False, True])
 def test_grouped_gemm_silu_gate(dev, rows, N, K, pair):
     _gemm_case(dev, rows, N, K, gated=True, pair=pair)
+
+
+@pytest.mark.parametrize("rows,N,K,gated", [([300, 0, 77, 129], 512, 512, False), ([4096], 1024, 4096, False),
+                                            ([1000, 513], 2816, 2048, True), ([700], 768, 256, False),
+                                            ([37] * 16, 2048, 1408, False), ([256, 255, 257], 1280, 64, True),
+                                            ([5000], 136, 72, False)])
+def test_grouped_gemm_wide_tiles(dev, rows, N, K, gated):
+    """512-column tiles (both TMEM accumulators per tile, second half's MMAs trailing the first):
+    also with an odd number of 256-column blocks, where the last tile's second half is past N."""
+    _gemm_case(dev, rows, N, K, gated=gated, pair=True, wide=1)
 
 
 def test_expert_op_reference_signature(dev):
