@@ -167,7 +167,16 @@ __device__ __forceinline__ void scan_groups(ControlSmem& c, int G, int lane, int
   }
 }
 
-__device__ __forceinline__ float silu_f(float g) { return g * __frcp_rn(1.0f + __expf(-g)); }
+// silu(g) = g * sigmoid(g) = 0.5 g * tanh(0.5 g) + 0.5 g: one special-function op (tanh.approx,
+// relative error about 2^-11, below the bf16 rounding of the result) and two FMAs per element.
+// (The IEEE-rounded reciprocal of the exp form made the gated epilogue six times slower than
+// the plain one: 12 us per 128 x 256 accumulator.)
+__device__ __forceinline__ float silu_f(float g) {
+  const float h = 0.5f * g;
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(h));
+  return fmaf(h, t, h);
+}
 
 // Reads a routing count.  On the device the table has been staged in shared memory (one
 // coalesced read of the peer-written table per CTA); the host build of these helpers

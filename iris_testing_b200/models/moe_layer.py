@@ -141,7 +141,10 @@ class MoELayer(nn.Module):
         self.l2_hints = tuple(int(v) for v in env.split(",")) if env else (0, 0)
         self.group_m = (0, 0)           # M-tiles per L2 chunk of the two GEMM kernels (0: automatic)
         self.tma_store = os.getenv("B200MOE_TMA_STORE", "1") != "0"   # hidden output through bulk tensor stores
-        self.wide_tiles = int(os.getenv("B200MOE_WIDE_TILES", "0"))   # 1: 512-column tiles in both GEMM kernels
+        # 512-column tiles (both TMEM accumulators per tile) in the first / second GEMM kernel:
+        # 1 on, 0 off; B200MOE_WIDE_TILES="w1,w2" overrides
+        env = os.getenv("B200MOE_WIDE_TILES")
+        self.wide_tiles = tuple(int(v) for v in env.split(",")) if env else (0, 0)
         self.drop_signal = False        # fault-injection aid for the timeout test
         self.profile = False            # record CUDA events between the phases of forward()
         self.phase_events = []
@@ -445,7 +448,7 @@ class MoELayer(nn.Module):
         ga.cta_pair = self._cta_pair
         ga.l2_hints = self.l2_hints[0]
         ga.tma_store = 0 if self.tma_store else -1
-        ga.wide_tiles = self.wide_tiles
+        ga.wide_tiles = self.wide_tiles[0]
         recv = self.recv[0]
         if cfg.gated:
             F = cfg.ffn_dim
@@ -462,7 +465,7 @@ class MoELayer(nn.Module):
             gb.status, gb.wait_budget_ns = status_p, self._budget_ns
             gb.cta_pair = self._cta_pair
             gb.l2_hints = self.l2_hints[1]
-            gb.wide_tiles = self.wide_tiles
+            gb.wide_tiles = self.wide_tiles[1]
             nv.check(lib.b200_grouped_gemm(ptr(self.hidden), self.cap_rows, ptr(self.w2), nv.EPI_COMBINE,
                                            0, C.byref(gb), None, C.byref(ca), None, self._ctas, st),
                      "GEMM2+combine launch")
