@@ -213,6 +213,146 @@ __global__ void plan_finalize_kernel(const int* __restrict__ topk_idx,
 }
 
 // ---------------------------------------------------------------------------
+// Small-token path: router AND plan in ONE single-CTA launch (instead of three launches).
+// For a few hundred tokens the layer is launch- and latency-bound, and the router GEMM on
+// tensor cores (TMEM allocation, barriers, 148 CTAs) costs more than the arithmetic: here one
+// warp per token forms the logits with 16-byte loads from the K-major router weights, the same
+// softmax / top-k code picks the experts, and the block then builds the plan in shared memory
+// (stable ranks per expert by ballot, scan, send order) and pushes the counts to the peers.
+// Limits (checked by the launcher): n_flat <= SMALL_MAX_FLAT, experts <= B200_MAX_EXPERTS.
+// ---------------------------------------------------------------------------
+constexpr int SMALL_MAX_FLAT = 4096;
+constexpr int SMALL_THREADS = 1024;
+
+__global__ void __launch_bounds__(SMALL_THREADS)
+route_plan_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr_kmajor,
+                        const float* __restrict__ bias, int T, int D, int E, int k, int renorm,
+                        int* __restrict__ topk_idx, float* __restrict__ topk_w, int* __restrict__ counts,
+                        int* __restrict__ bucket_start, int* __restrict__ send_order,
+                        int* __restrict__ dst_slot, PlanPushArgs push, int do_push) {
+  __shared__ float s_lg[SMALL_THREADS / 32][B200_MAX_EXPERTS];
+  __shared__ short s_idx[SMALL_MAX_FLAT];
+  __shared__ short s_rank[SMALL_MAX_FLAT];
+  __shared__ int s_cnt[B200_MAX_EXPERTS];
+  __shared__ int s_start[B200_MAX_EXPERTS + 1];
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
+  const int n_flat = T * k;
+  if (tid == 0) s_abort = 0;
+  // ---- router: one warp per token
+  float* lg = s_lg[warp];
+  const int d16 = D / 8;
+  for (int t = warp; t < T; t += nwarps) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * D);
+    for (int e = 0; e < E; ++e) {
+      const uint4* wrow = reinterpret_cast<const uint4*>(wr_kmajor + static_cast<size_t>(e) * D);
+      float acc = 0.f;
+      for (int i = lane; i < d16; i += 32) {
+        const uint4 xv = __ldg(xr + i), wv = __ldg(wrow + i);
+        const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&xv);
+        const __nv_bfloat162* wa = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = __bfloat1622float2(xa[j]), b = __bfloat1622float2(wa[j]);
+          acc = fmaf(a.x, b.x, acc);
+          acc = fmaf(a.y, b.y, acc);
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (lane == 0) lg[e] = acc + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) sum += __expf(lg[e] - mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    TopK tk; tk.init();
+    for (int e = lane; e < E; e += 32) tk.push(lg[e], e);
+    float wsum = 0.f, my_w = 0.f;
+    int my_i = 0;
+    for (int r = 0; r < k; ++r) {
+      float bv = tk.v[0]; int bi = tk.i[0] < 0 ? 0x7fffffff : tk.i[0];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (tk.i[0] == bi) {   // the winning lane pops its head
+#pragma unroll
+        for (int j = 0; j < ROUTER_MAX_K - 1; ++j) { tk.v[j] = tk.v[j + 1]; tk.i[j] = tk.i[j + 1]; }
+        tk.v[ROUTER_MAX_K - 1] = -INFINITY; tk.i[ROUTER_MAX_K - 1] = -1;
+      }
+      const float p = __expf(bv - mx) / sum;
+      wsum += p;
+      if (lane == r) { my_w = p; my_i = bi; }
+    }
+    if (lane < k) {
+      topk_idx[static_cast<size_t>(t) * k + lane] = my_i;
+      topk_w[static_cast<size_t>(t) * k + lane] = renorm ? my_w / wsum : my_w;
+      s_idx[t * k + lane] = static_cast<short>(my_i);
+    }
+    __syncwarp();
+  }
+  __syncthreads();
+  // ---- plan: stable rank of every routed copy inside its expert bucket
+  for (int e = warp; e < E; e += nwarps) {
+    int running = 0;
+    for (int base = 0; base < n_flat; base += 32) {
+      const int i = base + lane;
+      const bool hit = i < n_flat && s_idx[i] == e;
+      const unsigned b = __ballot_sync(0xffffffffu, hit);
+      if (hit) s_rank[i] = static_cast<short>(running + __popc(b & ((1u << lane) - 1u)));
+      running += __popc(b);
+    }
+    if (lane == 0) s_cnt[e] = running;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int acc = 0;
+    for (int e = 0; e < E; ++e) { s_start[e] = acc; acc += s_cnt[e]; }
+    s_start[E] = acc;
+  }
+  __syncthreads();
+  for (int e = tid; e <= E; e += blockDim.x) {
+    bucket_start[e] = s_start[e];
+    if (e < E) counts[e] = s_cnt[e];
+  }
+  for (int i = tid; i < n_flat; i += blockDim.x) {
+    const int pos = s_start[s_idx[i]] + s_rank[i];
+    send_order[pos] = i;
+    if (dst_slot) dst_slot[i] = pos;
+  }
+  if (do_push) {     // same protocol as plan_finalize_kernel
+    uint32_t epoch = push.epoch, need = push.need_iter_done;
+    unsigned long long off_counts = 0, off_flags = 0;
+    if (push.iter_ptr != nullptr) {
+      const uint32_t it = __ldcg(push.iter_ptr);
+      epoch = it + 1u;
+      need = it > 0u ? it - 1u : 0u;
+      if (it & 1u) { off_counts = push.stride_counts; off_flags = push.stride_flags; }
+    }
+    WaitCtx w; w.abort_flag = &s_abort; w.status = push.status; w.budget_ns = push.wait_budget_ns;
+    if (tid < push.world) wait_flag_geq(push.iter_done + tid, need, w, ST_TIMEOUT_ITER);
+    __syncthreads();
+    for (int p = 0; p < push.world; ++p) {
+      int* dst = reinterpret_cast<int*>(push.peer_counts[p] + off_counts) + push.rank * E;
+      for (int e = tid; e < E; e += blockDim.x) dst[e] = s_cnt[e];
+    }
+    __syncthreads();
+    if (tid < push.world) {
+      fence_acq_rel_sys();
+      st_release_sys(reinterpret_cast<uint32_t*>(push.peer_flags[tid] + off_flags) + push.rank, epoch);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Capacity of a padded exchange, computed on the device across all ranks (no host round
 // trip).  Every rank pushes its send_counts row ([dst][e]) into slot [rank] of a table on
 // every peer and stamps a flag with the epoch; once all flags show the epoch, each rank
@@ -348,6 +488,26 @@ int b200_pack_rows(const void* x, const int* send_order, int n_flat, int topk, i
 }
 
 }  // extern "C"
+
+// Router + plan of a small batch in one launch (see route_plan_small_kernel).  wr_kmajor is the
+// router matrix as [E, D]; outputs as b200_router_topk_simple + b200_plan.  Returns -2 when the
+// batch is too large for this path.
+extern "C" int b200_route_plan_small(const void* x, const void* wr_kmajor, const float* bias, int T, int D,
+                                     int E, int k, int renorm, int* topk_idx, float* topk_w, int* counts,
+                                     int* bucket_start, int* send_order, int* dst_slot,
+                                     const b200::PlanPushArgs* push, void* stream) {
+  if (k < 1 || k > b200::ROUTER_MAX_K || k > E || E < 1 || E > B200_MAX_EXPERTS || D % 8 != 0 || T < 0) return -1;
+  if (static_cast<long long>(T) * k > b200::SMALL_MAX_FLAT) return -2;
+  b200::PlanPushArgs pz;
+  memset(&pz, 0, sizeof(pz));
+  b200::route_plan_small_kernel<<<1, b200::SMALL_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(wr_kmajor), bias, T, D, E, k,
+      renorm, topk_idx, topk_w, counts, bucket_start, send_order, dst_slot, push ? *push : pz, push ? 1 : 0);
+  b200_count_launches(1);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int b200_route_plan_small_max_flat() { return b200::SMALL_MAX_FLAT; }
 
 extern "C" int b200_capacity(const int* send_counts, const b200::CapacityArgs* a, int* out, void* stream) {
   if (a == nullptr || a->world < 1 || a->world > B200_MAX_WORLD || a->e_local < 1 ||

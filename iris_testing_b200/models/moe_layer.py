@@ -38,7 +38,7 @@ from ..ops import cpu_ref
 from ..ops._common import declare, ptr, stream_ptr
 from ..ops.expert import sm_count
 from ..ops.plan import Plan, PlanPushArgs, make_plan
-from ..ops.router import router_topk
+from ..ops.router import router_kmajor, router_topk
 from ..utils import gen
 
 _NVTX = os.getenv("B200MOE_NVTX", "0") == "1"   # NVTX range around every forward
@@ -145,6 +145,7 @@ class MoELayer(nn.Module):
         # 1 on, 0 off; B200MOE_WIDE_TILES="w1,w2" overrides
         env = os.getenv("B200MOE_WIDE_TILES")
         self.wide_tiles = tuple(int(v) for v in env.split(",")) if env else (0, 0)
+        self.small_path = os.getenv("B200MOE_SMALL_PATH", "1") != "0"
         self.drop_signal = False        # fault-injection aid for the timeout test
         self.profile = False            # record CUDA events between the phases of forward()
         self.phase_events = []
@@ -215,6 +216,10 @@ class MoELayer(nn.Module):
             "b200_slot_reduce",
             [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint, C.c_int, C.c_int, C.c_int, C.c_void_p,
              C.POINTER(RetireArgs), C.c_void_p, C.c_ulonglong, C.c_void_p])
+        self._route_plan_small = declare(
+            "b200_route_plan_small",
+            [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(PlanPushArgs), C.c_void_p])
         self._ctas = int(self._num_ctas) if self._num_ctas else sm_count(dev)
         pair = cfg.cta_pair
         if pair is None:      # 256-row tiles pay off once an expert sees a few of them
@@ -335,10 +340,24 @@ class MoELayer(nn.Module):
             self.resize(max(int(needed_max * growth), self.cap_rows + BM))
         raise AssertionError("unreachable")
 
+    SMALL_MAX_FLAT = 4096          # routed copies the single-launch route+plan kernel takes
+    SMALL_MAX_MACS = 4 << 20       # tokens x hidden x experts up to which its CUDA-core router is the faster one
+
+    def uses_small_path(self, T: int) -> bool:
+        """True when a forward of ``T`` tokens takes the small-token path: router and plan in ONE
+        single-CTA launch instead of three launches."""
+        cfg = self.cfg
+        return (self.small_path and T * cfg.topk <= self.SMALL_MAX_FLAT
+                and T * cfg.hidden_dim * cfg.num_experts <= self.SMALL_MAX_MACS)
+
+    def launches_for(self, T: int) -> int:
+        """Kernel launches of one fused forward of ``T`` tokens: router + plan (3 launches, or 1 on
+        the small-token path), fused GEMM kernel(s), slot reduce."""
+        return (1 if self.uses_small_path(T) else 3) + (2 if self.cfg.gated else 1) + 1
+
     @property
     def launches_per_forward(self) -> int:
-        """Kernel launches of one fused forward: router, plan (2), fused GEMM kernel(s), slot reduce."""
-        return 6 if self.cfg.gated else 5
+        return self.launches_for(self.max_tokens)
 
     @property
     def status(self) -> torch.Tensor:
@@ -382,11 +401,6 @@ class MoELayer(nn.Module):
         if self.profile:
             self.phase_events = []
         ev("start")
-        # 1. router
-        idx, wgt = self.route(x)
-        ev("router")
-
-        # 2. plan (+ counts push)
         push = PlanPushArgs()
         push.world, push.rank = W, heap.rank
         push.iter_done = self.iter_done.data_ptr()
@@ -401,8 +415,25 @@ class MoELayer(nn.Module):
         n = T * k
         view = Plan(plan.counts, plan.bucket_start, plan.send_order[:n], plan.dst_slot[:n],
                     plan.rank_in_bucket[:n])
-        make_plan(idx, ET, out=view, push=push)
-        ev("plan")
+        if self.uses_small_path(T):
+            # 1+2. small batch: router and plan in one single-CTA launch
+            idx = torch.empty((T, k), dtype=torch.int32, device=x.device)
+            wgt = torch.empty((T, k), dtype=torch.float32, device=x.device)
+            bias = None if self.router_bias is None else self.router_bias.to(
+                device=x.device, dtype=torch.float32).contiguous()
+            nv.check(self._route_plan_small(ptr(x), ptr(router_kmajor(self.router)), ptr(bias), T, D, ET, k,
+                                            int(cfg.renormalize), ptr(idx), ptr(wgt), ptr(view.counts),
+                                            ptr(view.bucket_start), ptr(view.send_order), ptr(view.dst_slot),
+                                            C.byref(push), st), "route+plan launch")
+            ev("router")
+            ev("plan")
+        else:
+            # 1. router
+            idx, wgt = self.route(x)
+            ev("router")
+            # 2. plan (+ counts push)
+            make_plan(idx, ET, out=view, push=push)
+            ev("plan")
 
         # 3. dispatch + GEMM1 (one kernel)
         da = nv.DispatchArgs()

@@ -46,16 +46,22 @@ def _close(layer, x, y, ref=None):
     return ref
 
 
+@pytest.mark.parametrize("small", [True, False])
 @pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("D,F,E,k,gated,T", [
     (256, 512, 8, 2, True, 200), (256, 0, 4, 1, False, 77), (2048, 1408, 32, 4, True, 2048),
     (512, 256, 64, 8, True, 1000), (128, 0, 8, 2, False, 128), (1024, 1024, 2, 2, True, 3000),
     (128, 128, 128, 2, True, 700), (72, 128, 8, 3, True, 333), (200, 0, 16, 4, False, 129)])
-def test_fused_layer_matches_dense_reference(D, F, E, k, gated, T, pair):
+def test_fused_layer_matches_dense_reference(D, F, E, k, gated, T, pair, small):
+    """``small``: small batches may take the single-launch route+plan kernel; with it off every
+    shape goes through the tensor-core router and the two plan kernels."""
     from iris_testing_b200.config import MoEConfig
     from iris_testing_b200.utils import gen_local_tokens
     cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=E, topk=k, gated=gated, cta_pair=pair)
     layer, heap = _make(cfg, T)
+    layer.small_path = small
+    if small and not layer.uses_small_path(T // 2):
+        pytest.skip("this shape never takes the small-token path")
     dev = heap.device
     for i in range(3):                                  # exercises both parity slots and re-arming
         x = gen_local_tokens(1, T, D, torch.bfloat16, dev, i, 0, "normal")
@@ -197,6 +203,7 @@ def test_phase_timing_and_arrival_trace():
     from iris_testing_b200.utils import gen_local_tokens
     cfg = MoEConfig(hidden_dim=256, ffn_dim=512, num_experts=4, topk=2)
     layer, heap = _make(cfg, 1024)
+    layer.small_path = False              # time the router and the plan as separate phases
     x = gen_local_tokens(1, 1024, 256, torch.bfloat16, heap.device, 0, 0, "normal")
     layer(x)
     layer.profile = True
@@ -210,3 +217,35 @@ def test_phase_timing_and_arrival_trace():
     assert 0 <= rep["first_us"] <= rep["last_us"] and rep["own_last_published_us"] >= rep["own_first_published_us"]
     _close(layer, x, y)
     _finish(layer)
+
+
+def test_small_token_path_routes_and_plans_like_the_regular_kernels():
+    """The single-launch route+plan kernel must produce the same routing (indices exactly, weights
+    to fp32 rounding) and the same plan as the tensor-core router plus the two plan kernels,
+    and one launch fewer... two fewer."""
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.utils import gen_local_tokens, zipf_expert_bias
+    for D, F, E, k, T, bias in [(256, 512, 8, 2, 64, False), (512, 256, 64, 8, 100, True), (4096, 512, 8, 2, 64, False)]:
+        cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=E, topk=k)
+        layer, heap = _make(cfg, T)
+        if bias:
+            layer.router_bias = zipf_expert_bias(E, 1.2, device=heap.device)
+        x = gen_local_tokens(1, T, D, torch.bfloat16, heap.device, 4, 0, "normal")
+        assert layer.uses_small_path(T) and layer.launches_for(T) == 4
+        y_small = layer(x)
+        idx_s, w_s = (t.clone() for t in layer.last_routing)
+        order_s, slot_s = layer._plan.send_order[: T * k].clone(), layer._plan.dst_slot[: T * k].clone()
+        counts_s = layer._plan.counts.clone()
+        layer.small_path = False
+        assert layer.launches_for(T) == 6
+        y_reg = layer(x)
+        idx_r, w_r = layer.last_routing
+        from iris_testing_b200.ops import cpu_ref
+        clear = cpu_ref.clear_routing_mask(x, layer.router, k, layer.router_bias)
+        assert torch.equal(idx_s[clear], idx_r[clear]) and torch.allclose(w_s[clear], w_r[clear], atol=1e-6, rtol=2e-4)
+        if bool(clear.all()):
+            assert torch.equal(order_s, layer._plan.send_order[: T * k]) and torch.equal(slot_s, layer._plan.dst_slot[: T * k])
+            assert torch.equal(counts_s, layer._plan.counts)
+        _close(layer, x, y_small)
+        _close(layer, x, y_reg)
+        _finish(layer)
