@@ -898,9 +898,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
           if (mt >= da.cap_mtiles) {
             report_status(w.status, ST_BAD_INDEX);
           } else if (stored > 0) {
-            fence_acq_rel_sys();
-            red_add_release_sys(reinterpret_cast<uint32_t*>(da.peer_ready[dst]) + mt,
-                                static_cast<uint32_t>(stored));
+            uint32_t* ctr = reinterpret_cast<uint32_t*>(da.peer_ready[dst]) + mt;
+            if (dst == da.rank) {       // rows and counter are in this GPU's memory
+              fence_acq_rel_gpu();
+              red_add_release_gpu(ctr, static_cast<uint32_t>(stored));
+            } else {
+              fence_acq_rel_sys();
+              red_add_release_sys(ctr, static_cast<uint32_t>(stored));
+            }
             if (da.trace != nullptr && dst == da.rank && mt < da.trace_tiles)
               da.trace[2 + da.trace_tiles + mt] = globaltimer_ns();
           }

@@ -244,23 +244,35 @@ route_plan_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   const int d16 = D / 8;
   for (int t = warp; t < T; t += nwarps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * D);
-    for (int e = 0; e < E; ++e) {
-      const uint4* wrow = reinterpret_cast<const uint4*>(wr_kmajor + static_cast<size_t>(e) * D);
-      float acc = 0.f;
+    // Experts in groups of four with independent accumulators: the (cold) weight and token loads
+    // of a group are all in flight together instead of one dependent pair at a time.
+    for (int e0 = 0; e0 < E; e0 += 4) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
       for (int i = lane; i < d16; i += 32) {
-        const uint4 xv = __ldg(xr + i), wv = __ldg(wrow + i);
+        const uint4 xv = __ldg(xr + i);
+        uint4 wv[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          wv[j] = __ldg(reinterpret_cast<const uint4*>(wr_kmajor + static_cast<size_t>(min(e0 + j, E - 1)) * D) + i);
         const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&xv);
-        const __nv_bfloat162* wa = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float2 a = __bfloat1622float2(xa[j]), b = __bfloat1622float2(wa[j]);
-          acc = fmaf(a.x, b.x, acc);
-          acc = fmaf(a.y, b.y, acc);
+          const __nv_bfloat162* wa = reinterpret_cast<const __nv_bfloat162*>(&wv[j]);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 a = __bfloat1622float2(xa[q]), b = __bfloat1622float2(wa[q]);
+            acc[j] = fmaf(a.x, b.x, acc[j]);
+            acc[j] = fmaf(a.y, b.y, acc[j]);
+          }
         }
       }
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (lane == 0) lg[e] = acc + (bias ? bias[e] : 0.f);
+      for (int j = 0; j < 4; ++j) {
+        float a = acc[j];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+        if (lane == 0 && e0 + j < E) lg[e0 + j] = a + (bias ? bias[e0 + j] : 0.f);
+      }
     }
     __syncwarp();
     float mx = -INFINITY;

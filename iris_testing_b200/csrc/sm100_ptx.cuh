@@ -76,6 +76,14 @@ __device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void fence_acq_rel_sys() {
   asm volatile("fence.acq_rel.sys;" ::: "memory");
 }
+// GPU-scope variants for a flag that lives in this GPU's own memory and is written by this GPU:
+// cheaper than the system-scope forms, and still observed by a system-scope acquire load here.
+__device__ __forceinline__ void fence_acq_rel_gpu() {
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+}
+__device__ __forceinline__ void red_add_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 // Orders generic-proxy accesses against async-proxy (TMA) accesses.
 __device__ __forceinline__ void fence_proxy_async() {
   asm volatile("fence.proxy.async;" ::: "memory");
