@@ -6,11 +6,16 @@ copies the reference to a temporary directory, adds a packaging stub that lists 
 top-level modules (no source file is touched), installs that copy with ``--no-deps`` and
 verifies that the installed modules are byte-identical to the reference's.
 
-    python baseline/install_reference.py [/path/to/reference]
+    python baseline/install_reference.py [/path/to/reference] [--find-links DIR]
+
+The wheel directory pip may look into comes from ``--find-links``, else from the
+``PIP_FIND_LINKS`` environment variable; with neither, pip is run without one (the install
+needs no wheels: it uses ``--no-deps``).
 """
 from __future__ import annotations
 
 import filecmp
+import os
 import shutil
 import subprocess
 import sys
@@ -27,12 +32,15 @@ setup(name="iris_testing_reference", version="0.0.0", py_modules=%r)
 ''' % (MODULES,)
 
 
-def install(reference: Path) -> str | None:
+def install(reference: Path, find_links: str | None = None) -> str | None:
     """Returns None on success, else a one-line reason."""
     if not (reference / "baseline.py").exists():
         return f"no reference tree at {reference}"
-    pip = [sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation",
-           "--find-links", "/opt/wheelhouse", "--target", str(TARGET)]
+    links = find_links or os.environ.get("PIP_FIND_LINKS")
+    pip = [sys.executable, "-m", "pip", "install", "--no-index", "--no-build-isolation"]
+    if links:
+        pip += ["--find-links", links.split()[0]]
+    pip += ["--target", str(TARGET)]
     first = subprocess.run(pip + [str(reference)], capture_output=True, text=True)
     if first.returncode != 0:
         with tempfile.TemporaryDirectory() as tmp:
@@ -53,7 +61,13 @@ def install(reference: Path) -> str | None:
 
 
 if __name__ == "__main__":
-    ref = Path(sys.argv[1]) if len(sys.argv) > 1 else HERE.parent.parent / "reference"
-    err = install(ref)
+    argv = sys.argv[1:]
+    links = None
+    if "--find-links" in argv:
+        i = argv.index("--find-links")
+        links = argv[i + 1]
+        del argv[i:i + 2]
+    ref = Path(argv[0]) if argv else HERE.parent.parent / "reference"
+    err = install(ref, links)
     print("ok" if err is None else f"failed: {err}")
     sys.exit(0 if err is None else 1)
