@@ -249,3 +249,19 @@ def test_small_token_path_routes_and_plans_like_the_regular_kernels():
         _close(layer, x, y_small)
         _close(layer, x, y_reg)
         _finish(layer)
+
+
+@pytest.mark.parametrize("wide", [(1, 1), (0, 1)])
+@pytest.mark.parametrize("D,F,E,k,gated,T", [(512, 1024, 4, 2, True, 2100), (768, 0, 2, 2, False, 1500)])
+def test_fused_layer_with_wide_tiles(D, F, E, k, gated, T, wide):
+    """The optional 512-column tile geometry in the fused kernels (dispatch + GEMM1 and GEMM2 +
+    combine): odd numbers of 256-column blocks, ragged groups, both parities."""
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.utils import gen_local_tokens
+    cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=E, topk=k, gated=gated, cta_pair=True)
+    layer, heap = _make(cfg, T)
+    layer.wide_tiles = wide
+    for i in range(3):
+        x = gen_local_tokens(1, T, D, torch.bfloat16, heap.device, 10 + i, 0, "normal")
+        _close(layer, x, layer(x))
+    _finish(layer)
