@@ -11,6 +11,7 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <algorithm>
 #include <atomic>
 
 #include "moe_args.h"
@@ -213,50 +214,57 @@ __global__ void plan_finalize_kernel(const int* __restrict__ topk_idx,
 }
 
 // ---------------------------------------------------------------------------
-// Small-token path: router AND plan in ONE single-CTA launch (instead of three launches).
-// For a few hundred tokens the layer is launch- and latency-bound, and the router GEMM on
-// tensor cores (TMEM allocation, barriers, 148 CTAs) costs more than the arithmetic: here one
-// warp per token forms the logits with 16-byte loads from the K-major router weights, the same
-// softmax / top-k code picks the experts, and the block then builds the plan in shared memory
+// Small-token path: router AND plan in ONE launch (instead of three launches).
+// For a few thousand routed copies the layer is launch- and latency-bound, and the router GEMM on
+// tensor cores (TMEM allocation, barriers, 148 CTAs) costs more than the arithmetic.  Here one warp
+// per token forms the logits with 16-byte loads from the K-major router weights (tokens spread
+// over as many CTAs as there are groups of eight tokens, so that the cold loads of a wide hidden
+// dimension run in parallel), the same softmax / top-k code picks the experts, and the CTA that
+// finishes LAST (a ticket in global memory; nobody waits) builds the plan in shared memory
 // (stable ranks per expert by ballot, scan, send order) and pushes the counts to the peers.
 // Limits (checked by the launcher): n_flat <= SMALL_MAX_FLAT, experts <= B200_MAX_EXPERTS.
 // ---------------------------------------------------------------------------
 constexpr int SMALL_MAX_FLAT = 4096;
-constexpr int SMALL_THREADS = 1024;
+constexpr int SMALL_THREADS = 256;
+constexpr int SMALL_EG = 8;            // experts per pass over a token's row
 
 __global__ void __launch_bounds__(SMALL_THREADS)
 route_plan_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ wr_kmajor,
                         const float* __restrict__ bias, int T, int D, int E, int k, int renorm,
                         int* __restrict__ topk_idx, float* __restrict__ topk_w, int* __restrict__ counts,
                         int* __restrict__ bucket_start, int* __restrict__ send_order,
-                        int* __restrict__ dst_slot, PlanPushArgs push, int do_push) {
+                        int* __restrict__ dst_slot, PlanPushArgs push, int do_push, unsigned int* ticket) {
   __shared__ float s_lg[SMALL_THREADS / 32][B200_MAX_EXPERTS];
   __shared__ short s_idx[SMALL_MAX_FLAT];
   __shared__ short s_rank[SMALL_MAX_FLAT];
   __shared__ int s_cnt[B200_MAX_EXPERTS];
   __shared__ int s_start[B200_MAX_EXPERTS + 1];
   __shared__ int s_abort;
+  __shared__ int s_last;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
   const int n_flat = T * k;
   if (tid == 0) s_abort = 0;
   // ---- router: one warp per token
   float* lg = s_lg[warp];
   const int d16 = D / 8;
-  for (int t = warp; t < T; t += nwarps) {
+  for (int t = blockIdx.x * nwarps + warp; t < T; t += gridDim.x * nwarps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * D);
-    // Experts in groups of four with independent accumulators: the (cold) weight and token loads
-    // of a group are all in flight together instead of one dependent pair at a time.
-    for (int e0 = 0; e0 < E; e0 += 4) {
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    // Experts in groups of eight with independent accumulators, two 16-byte pieces of the row per
+    // trip: 18 (cold) loads are in flight together instead of one dependent pair at a time.
+    for (int e0 = 0; e0 < E; e0 += SMALL_EG) {
+      float acc[SMALL_EG];
+#pragma unroll
+      for (int j = 0; j < SMALL_EG; ++j) acc[j] = 0.f;
+#pragma unroll 2
       for (int i = lane; i < d16; i += 32) {
         const uint4 xv = __ldg(xr + i);
-        uint4 wv[4];
+        uint4 wv[SMALL_EG];
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < SMALL_EG; ++j)
           wv[j] = __ldg(reinterpret_cast<const uint4*>(wr_kmajor + static_cast<size_t>(min(e0 + j, E - 1)) * D) + i);
         const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < SMALL_EG; ++j) {
           const __nv_bfloat162* wa = reinterpret_cast<const __nv_bfloat162*>(&wv[j]);
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -267,7 +275,7 @@ route_plan_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
         }
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
+      for (int j = 0; j < SMALL_EG; ++j) {
         float a = acc[j];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
@@ -307,9 +315,23 @@ route_plan_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
     if (lane < k) {
       topk_idx[static_cast<size_t>(t) * k + lane] = my_i;
       topk_w[static_cast<size_t>(t) * k + lane] = renorm ? my_w / wsum : my_w;
-      s_idx[t * k + lane] = static_cast<short>(my_i);
     }
     __syncwarp();
+  }
+  // ---- hand-over: every CTA publishes its choices and takes a ticket; the last one plans
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned int prev = atomicAdd(ticket, 1u);
+    s_last = prev == gridDim.x - 1u;
+    if (s_last) *ticket = 0u;          // re-armed for the next launch on this stream
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int i = tid; i < n_flat; i += blockDim.x) {
+    const int e = __ldcg(topk_idx + i);
+    s_idx[i] = static_cast<short>(min(max(e, 0), E - 1));
   }
   __syncthreads();
   // ---- plan: stable rank of every routed copy inside its expert bucket
@@ -502,19 +524,25 @@ int b200_pack_rows(const void* x, const int* send_order, int n_flat, int topk, i
 }  // extern "C"
 
 // Router + plan of a small batch in one launch (see route_plan_small_kernel).  wr_kmajor is the
-// router matrix as [E, D]; outputs as b200_router_topk_simple + b200_plan.  Returns -2 when the
-// batch is too large for this path.
+// router matrix as [E, D]; outputs as b200_router_topk_simple + b200_plan.  `ticket` is one zeroed
+// word of device memory owned by the caller (launches that may overlap need separate words); the
+// kernel leaves it zero.  Returns -2 when the batch is too large for this path.
 extern "C" int b200_route_plan_small(const void* x, const void* wr_kmajor, const float* bias, int T, int D,
                                      int E, int k, int renorm, int* topk_idx, float* topk_w, int* counts,
                                      int* bucket_start, int* send_order, int* dst_slot,
-                                     const b200::PlanPushArgs* push, void* stream) {
-  if (k < 1 || k > b200::ROUTER_MAX_K || k > E || E < 1 || E > B200_MAX_EXPERTS || D % 8 != 0 || T < 0) return -1;
+                                     const b200::PlanPushArgs* push, unsigned int* ticket, void* stream) {
+  if (k < 1 || k > b200::ROUTER_MAX_K || k > E || E < 1 || E > B200_MAX_EXPERTS || D % 8 != 0 || T < 0 ||
+      ticket == nullptr)
+    return -1;
   if (static_cast<long long>(T) * k > b200::SMALL_MAX_FLAT) return -2;
   b200::PlanPushArgs pz;
   memset(&pz, 0, sizeof(pz));
-  b200::route_plan_small_kernel<<<1, b200::SMALL_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+  const int warps = b200::SMALL_THREADS / 32;
+  const int grid = std::max(1, std::min((T + warps - 1) / warps, 148));
+  b200::route_plan_small_kernel<<<grid, b200::SMALL_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(wr_kmajor), bias, T, D, E, k,
-      renorm, topk_idx, topk_w, counts, bucket_start, send_order, dst_slot, push ? *push : pz, push ? 1 : 0);
+      renorm, topk_idx, topk_w, counts, bucket_start, send_order, dst_slot, push ? *push : pz, push ? 1 : 0,
+      ticket);
   b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }

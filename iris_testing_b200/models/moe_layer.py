@@ -219,7 +219,9 @@ class MoELayer(nn.Module):
         self._route_plan_small = declare(
             "b200_route_plan_small",
             [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
-             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(PlanPushArgs), C.c_void_p])
+             C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.POINTER(PlanPushArgs), C.c_void_p,
+             C.c_void_p])
+        self._small_ticket = torch.zeros(1, dtype=torch.int32, device=dev)   # "last CTA plans" hand-over word
         self._ctas = int(self._num_ctas) if self._num_ctas else sm_count(dev)
         pair = cfg.cta_pair
         if pair is None:      # 256-row tiles pay off once an expert sees a few of them
@@ -296,6 +298,7 @@ class MoELayer(nn.Module):
         self.arrived.zero_()
         self.ready.zero_()
         self.ticket.zero_()
+        self._small_ticket.zero_()
         self.heap.status.zero_()
         torch.cuda.synchronize(self.heap.device)
         if W > 1:
@@ -341,11 +344,11 @@ class MoELayer(nn.Module):
         raise AssertionError("unreachable")
 
     SMALL_MAX_FLAT = 4096          # routed copies the single-launch route+plan kernel takes
-    SMALL_MAX_MACS = 4 << 20       # tokens x hidden x experts up to which its CUDA-core router is the faster one
+    SMALL_MAX_MACS = 64 << 20      # tokens x hidden x experts up to which its CUDA-core router is the faster one
 
     def uses_small_path(self, T: int) -> bool:
         """True when a forward of ``T`` tokens takes the small-token path: router and plan in ONE
-        single-CTA launch instead of three launches."""
+        launch instead of three."""
         cfg = self.cfg
         return (self.small_path and T * cfg.topk <= self.SMALL_MAX_FLAT
                 and T * cfg.hidden_dim * cfg.num_experts <= self.SMALL_MAX_MACS)
@@ -424,7 +427,7 @@ class MoELayer(nn.Module):
             nv.check(self._route_plan_small(ptr(x), ptr(router_kmajor(self.router)), ptr(bias), T, D, ET, k,
                                             int(cfg.renormalize), ptr(idx), ptr(wgt), ptr(view.counts),
                                             ptr(view.bucket_start), ptr(view.send_order), ptr(view.dst_slot),
-                                            C.byref(push), st), "route+plan launch")
+                                            C.byref(push), ptr(self._small_ticket), st), "route+plan launch")
             ev("router")
             ev("plan")
         else:
