@@ -26,7 +26,7 @@ class MoEConfig:
     capacity_factor: Optional[float] = 1.25   # receive capacity over the balanced load; None: worst case
                                               # (every routed copy of every rank), world_size x the memory
     wait_budget_ms: float = 2000.0  # budget of every bounded device-side wait
-    cta_pair: Optional[bool] = None  # two CTAs per MMA (cta_group::2); None: when experts average >= 256 rows
+    cta_pair: Optional[bool] = None  # two CTAs per MMA (cta_group::2); None: when experts average >= 128 rows
 
     def __post_init__(self) -> None:
         if self.num_experts % self.world_size != 0:

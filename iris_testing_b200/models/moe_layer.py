@@ -224,8 +224,13 @@ class MoELayer(nn.Module):
         self._small_ticket = torch.zeros(1, dtype=torch.int32, device=dev)   # "last CTA plans" hand-over word
         self._ctas = int(self._num_ctas) if self._num_ctas else sm_count(dev)
         pair = cfg.cta_pair
-        if pair is None:      # 256-row tiles pay off once an expert sees a few of them
-            pair = (T * k * W) // max(ET, 1) >= 256
+        if os.getenv("B200MOE_CTA_PAIR", "") in ("0", "1"):       # override for tile-shape experiments
+            pair = os.environ["B200MOE_CTA_PAIR"] == "1"
+        if pair is None:
+            # 256-row tiles pay off once experts average 128 rows: from there on many experts hold more than
+            # one 128-row tile, and a second tile streams the expert's weights again (Mixtral shape, one GPU:
+            # 700 -> 666 us at 128 rows per expert, 773 -> 670 us at 192; 555 -> 643 us at 64)
+            pair = (T * k * W) // max(ET, 1) >= 128
         self._cta_pair = int(bool(pair))
         self._budget_ns = int(cfg.wait_budget_ms * 1e6)
         self.recv = self.meta = self.ready = self.hidden = None

@@ -45,7 +45,7 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     group_rows int32 [G] on the device (rows per group; sum <= M)
     group_m    M-tiles per L2-blocking chunk; 0 picks about 48 MB of activations per chunk.
     cta_pair   True: two CTAs per MMA (tcgen05 cta_group::2, 256-row tiles); None picks it
-               when the groups average at least 256 rows.
+               when the groups average at least 128 rows.
     wide_tiles CTA pairs only: 512-column tiles that use both TMEM accumulators at once (25 % fewer
                operand bytes per FLOP, but the epilogue is no longer hidden); 1 = on, 0 = off (default).
     epilogue   EPI_STORE -> out [M, N];  EPI_SILU_GATE -> out [M, N/2] where every
@@ -91,7 +91,7 @@ def grouped_gemm(a: torch.Tensor, w_kmajor: torch.Tensor, group_rows: torch.Tens
     ga.status = status.data_ptr()
     ga.wait_budget_ns = int(wait_budget_ms * 1e6)
     if cta_pair is None:
-        cta_pair = M >= 256 * G
+        cta_pair = M >= 128 * G
     ga.cta_pair = int(bool(cta_pair))
     ga.l2_hints = int(l2_hints)
     ga.wide_tiles = int(wide_tiles)
