@@ -265,3 +265,45 @@ def test_fused_layer_with_wide_tiles(D, F, E, k, gated, T, wide):
         x = gen_local_tokens(1, T, D, torch.bfloat16, heap.device, 10 + i, 0, "normal")
         _close(layer, x, layer(x))
     _finish(layer)
+
+
+def test_random_layer_shapes_match_dense_reference():
+    """Seeded sweep over odd shapes: hidden sizes that are no multiple of a k-block, one to 128
+    experts, top-1 to top-8, one token to a few thousand, every tile geometry, with and without
+    the small-token path, capacity factor and skewed routing.  Each case: two full steps and a
+    shorter one through ``forward_checked`` against the dense oracle, then status and guards."""
+    import random
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.ops import cpu_ref
+    from iris_testing_b200.utils import gen_local_tokens, zipf_expert_bias
+    rng = random.Random(20240607)
+    for case in range(120):
+        gated = rng.random() < 0.6
+        D = rng.choice([8, 64, 72, 128, 200, 256, 520, 1024, 2048])
+        F = rng.choice([128, 256, 384, 1408]) if gated else rng.choice([0, 8, 64, 200, 256, 1000])
+        E = rng.choice([1, 2, 3, 5, 8, 24, 64, 128])
+        k = rng.randint(1, min(E, 8))
+        T = rng.choice([1, 2, 17, 64, 127, 128, 129, 255, 257, 1000, 2047])
+        cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=E, topk=k, gated=gated,
+                        cta_pair=rng.choice([None, True, False]), capacity_factor=rng.choice([None, 1.25]))
+        layer, heap = _make(cfg, T)
+        layer.small_path = rng.random() < 0.7
+        layer.wide_tiles = rng.choice([(0, 0), (0, 0), (1, 1)])
+        if rng.random() < 0.3:
+            layer.router_bias = zipf_expert_bias(E, 1.2, scale=3.0, device=heap.device)
+        what = (case, D, F, E, k, T, gated, cfg.cta_pair, cfg.capacity_factor, layer.small_path, layer.wide_tiles)
+        for i in range(2):
+            x = gen_local_tokens(1, T, D, torch.bfloat16, heap.device, i, 0, "normal")
+            y = layer.forward_checked(x)
+            ref = _dense(layer, x)
+            clear = cpu_ref.clear_routing_mask(x, layer.router, k, layer.router_bias)
+            scale = float(ref.abs().max()) or 1.0
+            err = float((y.float() - ref)[clear].abs().max()) if bool(clear.any()) else 0.0
+            assert err <= TOL * scale, (what, err, scale)
+        half = max(T // 2, 1)
+        y = layer.forward_checked(x[:half])
+        err = float((y.float() - ref[:half])[clear[:half]].abs().max()) if bool(clear[:half].any()) else 0.0
+        assert err <= TOL * scale, (what, err, scale)
+        _finish(layer)
+        del layer
+        heap.close()
