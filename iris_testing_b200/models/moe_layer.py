@@ -309,6 +309,26 @@ class MoELayer(nn.Module):
         if W > 1:
             dist.barrier(group=self.heap.group)
 
+    def close(self) -> None:
+        """Collective: give this layer's symmetric buffers back to the heap (every rank, between
+        steps, in the same order for layers that share a heap).  The layer cannot run afterwards."""
+        if getattr(self, "_closed", False) or self.heap is None or not getattr(self, "_engine_ready", False):
+            return
+        W = self.cfg.world_size
+        torch.cuda.synchronize(self.heap.device)
+        if W > 1:
+            dist.barrier(group=self.heap.group)          # nobody is still writing into a peer
+        if not self.heap.closed:
+            for t in [*reversed(self._canaries), self.ready, self.meta, self.recv, self.out_slots,
+                      self.arrived, self.iter_done, self.counts_flag, self.counts_all]:
+                if t is not None:
+                    self.heap.free(t)
+        self._canaries = []
+        self.recv = self.meta = self.ready = self.out_slots = self.hidden = None
+        self.arrived = self.iter_done = self.counts_flag = self.counts_all = None
+        self._graph = None
+        self._closed = True
+
     def resize(self, cap_rows: int) -> None:
         """Collective: re-make the receive buffers for ``cap_rows`` rows per rank (rounded up to
         a tile).  Every rank must call it with the same value, between steps."""

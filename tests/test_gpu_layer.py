@@ -307,3 +307,32 @@ def test_random_layer_shapes_match_dense_reference():
         _finish(layer)
         del layer
         heap.close()
+
+
+def test_layer_close_returns_its_symmetric_buffers():
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.models import MoELayer
+    from iris_testing_b200.parallel.symm import SymmetricHeap
+    from iris_testing_b200.utils import gen_local_tokens
+    torch.cuda.set_device(0)
+    heap = SymmetricHeap(64 << 20)
+    used0 = heap.bytes_in_use
+    first = None
+    for D, E in ((256, 8), (512, 4), (256, 8)):
+        cfg = MoEConfig(hidden_dim=D, ffn_dim=256, num_experts=E, topk=2)
+        layer = MoELayer(cfg, max_tokens=300, heap=heap, router_std=None, debug_canaries=True)
+        assert heap.bytes_in_use > used0
+        if first is None:
+            first = layer.counts_all.data_ptr()
+        x = gen_local_tokens(1, 300, D, torch.bfloat16, heap.device, 0, 0, "normal")
+        _close(layer, x, layer(x))
+        _finish(layer)
+        layer.close()
+        layer.close()                                     # a second call is a no-op
+        assert heap.bytes_in_use == used0
+    # the space was reused, not appended
+    cfg = MoEConfig(hidden_dim=256, ffn_dim=256, num_experts=8, topk=2)
+    layer = MoELayer(cfg, max_tokens=300, heap=heap, router_std=None, debug_canaries=True)
+    assert layer.counts_all.data_ptr() == first
+    layer.close()
+    heap.close()

@@ -233,6 +233,54 @@ def test_skewed_layers(heap, D: int, F: int, e_local: int, topk: int, T: int) ->
     tight.check_status()
 
 
+def test_random_layers(heap, cases: int, seed: int) -> None:
+    """Seeded sweep of layer shapes across the ranks (every rank draws the same shapes; token counts
+    differ per rank, some ranks get none): ``forward_checked`` against the dense oracle over the
+    gathered weights, then the layer's buffers go back to the shared heap."""
+    import random
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.models import MoELayer
+    from iris_testing_b200.ops import cpu_ref
+    from iris_testing_b200.utils import gen_local_tokens, zipf_expert_bias
+    world, rank, dev = heap.world, heap.rank, heap.device
+    rng = random.Random(seed)
+    used0 = heap.bytes_in_use
+    for case in range(cases):
+        gated = rng.random() < 0.6
+        D = rng.choice([8, 72, 128, 256, 520, 1024])
+        F = rng.choice([128, 256, 384, 1408]) if gated else rng.choice([0, 8, 200, 256])
+        e_local = rng.choice([1, 2, 3, 8, 16])
+        E = e_local * world
+        k = rng.randint(1, min(E, 8))
+        T = rng.choice([1, 17, 64, 128, 129, 257, 1000])
+        t_rank = [rng.choice([T, T, T // 2, 0]) for _ in range(world)]
+        cfg = MoEConfig(hidden_dim=D, ffn_dim=F, num_experts=E, topk=k, world_size=world, gated=gated,
+                        cta_pair=rng.choice([None, True, False]), capacity_factor=rng.choice([None, 1.25]))
+        layer = MoELayer(cfg, max_tokens=T, heap=heap, router_std=None, debug_canaries=True)
+        layer.small_path = rng.random() < 0.7
+        if rng.random() < 0.3:
+            layer.router_bias = zipf_expert_bias(E, 1.2, scale=3.0, device=dev)
+        w1, w3, w2 = layer.reference_weights()
+        if gated:
+            ws = dict(w1=torch.cat(_gather(w1)), w3=torch.cat(_gather(w3)), w2=torch.cat(_gather(w2)),
+                      round_hidden=torch.bfloat16)
+        else:
+            ws = dict(w_single=torch.cat(_gather(w1)))
+        for i in range(2):
+            x = gen_local_tokens(1, T, D, torch.bfloat16, dev, i, rank, "normal")[: t_rank[rank]]
+            y = layer.forward_checked(x)
+            if x.shape[0]:
+                ref = cpu_ref.dense_moe_ref(x, layer.router, k, bias=layer.router_bias, **ws)
+                clear = cpu_ref.clear_routing_mask(x, layer.router, k, layer.router_bias)
+                scale = float(ref.abs().max()) or 1.0
+                err = float((y.float() - ref)[clear].abs().max()) if bool(clear.any()) else 0.0
+                assert err <= 1e-2 * scale, (rank, case, (D, F, E, k, T, t_rank, gated), err, scale)
+        layer.check_status()
+        layer.check_canaries()
+        layer.close()
+        assert heap.bytes_in_use == used0, (rank, case)
+
+
 def _worker(rank: int, world: int) -> None:
     from iris_testing_b200.parallel.symm import SymmetricHeap
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -260,6 +308,9 @@ def _worker(rank: int, world: int) -> None:
     say("test_fused_layer(many experts) PASSED")
     test_skewed_layers(heap, D=256, F=256, e_local=2, topk=2, T=256)
     say("test_skewed_layers(all-to-one, empty rank, capacity growth) PASSED")
+    cases = int(os.getenv("RANDOM_LAYER_CASES", "24"))
+    test_random_layers(heap, cases=cases, seed=int(os.getenv("RANDOM_LAYER_SEED", "7")))
+    say(f"test_random_layers({cases} shapes, uneven token counts) PASSED")
     dist.barrier()
     dist.destroy_process_group()
     say("ALL PASSED")
