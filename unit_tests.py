@@ -182,7 +182,9 @@ def test_padded_engine(heap, e_local: int, H: int, T: int, topk: int, copy_mode:
         a2a.send_back()
         y = a2a.reduce(plan, idx, wgt)
         ref = x.float() * wgt.sum(dim=1, keepdim=True)
-        assert torch.allclose(y.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2), rank
+        assert y.shape == ref.shape, (rank, y.shape, ref.shape)
+        if ref.numel():                                   # a rank may hold no token in some exchange
+            assert torch.allclose(y.float(), ref, atol=2e-2 * float(ref.abs().max()), rtol=2e-2), rank
     heap.check_status()
 
 
@@ -300,6 +302,10 @@ def _worker(rank: int, world: int) -> None:
     for mode in ("stores", "bulk"):
         test_padded_engine(heap, e_local=4, H=512, T=600, topk=2, copy_mode=mode)
         say(f"test_padded_engine({mode}) PASSED")
+    for e_local, H, T, topk, mode in ((1, 8, 1, 1, "stores"), (3, 72, 33, 2, "bulk"), (5, 520, 257, 3, "stores"),
+                                      (8, 1024, 2000, 4, "bulk"), (2, 4096, 64, 2, "stores")):
+        test_padded_engine(heap, e_local=e_local, H=H, T=T, topk=topk, copy_mode=mode)
+    say("test_padded_engine(odd shapes: one token, 8-byte-wide rows, 5 experts per rank, ...) PASSED")
     test_fused_layer(heap, D=256, F=512, e_local=2, topk=2, T=300)
     say("test_fused_layer(gated) PASSED")
     test_fused_layer(heap, D=256, F=0, e_local=4, topk=1, T=77)
