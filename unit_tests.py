@@ -305,7 +305,7 @@ def _worker(rank: int, world: int) -> None:
     for e_local, H, T, topk, mode in ((1, 8, 1, 1, "stores"), (3, 72, 33, 2, "bulk"), (5, 520, 257, 3, "stores"),
                                       (8, 1024, 2000, 4, "bulk"), (2, 4096, 64, 2, "stores")):
         test_padded_engine(heap, e_local=e_local, H=H, T=T, topk=topk, copy_mode=mode)
-    say("test_padded_engine(odd shapes: one token, 8-byte-wide rows, 5 experts per rank, ...) PASSED")
+    say("test_padded_engine(odd shapes: one token, 16-byte rows, five experts per rank, empty ranks) PASSED")
     test_fused_layer(heap, D=256, F=512, e_local=2, topk=2, T=300)
     say("test_fused_layer(gated) PASSED")
     test_fused_layer(heap, D=256, F=0, e_local=4, topk=1, T=77)
