@@ -369,14 +369,19 @@ class MoELayer(nn.Module):
         raise AssertionError("unreachable")
 
     SMALL_MAX_FLAT = 4096          # routed copies the single-launch route+plan kernel takes
-    SMALL_MAX_MACS = 64 << 20      # tokens x hidden x experts up to which its CUDA-core router is the faster one
+    SMALL_MAX_TRIPS = 16           # dependent load round trips per warp up to which its CUDA-core router wins
 
     def uses_small_path(self, T: int) -> bool:
         """True when a forward of ``T`` tokens takes the small-token path: router and plan in ONE
-        launch instead of three."""
+        launch instead of three.  The kernel gives every token a warp (eight per CTA, at most 148
+        CTAs) that walks the token's row once per group of eight experts, two 16-byte pieces per
+        lane and trip; the Mixtral shape at 2048 tokens (16 trips) is where it stops being faster
+        than the tensor-core router plus the two plan kernels."""
         cfg = self.cfg
-        return (self.small_path and T * cfg.topk <= self.SMALL_MAX_FLAT
-                and T * cfg.hidden_dim * cfg.num_experts <= self.SMALL_MAX_MACS)
+        if not self.small_path or T * cfg.topk > self.SMALL_MAX_FLAT:
+            return False
+        trips = (-(-T // (148 * 8))) * (-(-cfg.num_experts // 8)) * (-(-cfg.hidden_dim // (8 * 64)))
+        return trips <= self.SMALL_MAX_TRIPS
 
     def launches_for(self, T: int) -> int:
         """Kernel launches of one fused forward of ``T`` tokens: router + plan (3 launches, or 1 on
