@@ -420,6 +420,8 @@ class MoELayer(nn.Module):
         cfg, heap = self.cfg, self.heap
         W, EL, ET, k, D = cfg.world_size, cfg.e_local, cfg.num_experts, cfg.topk, cfg.hidden_dim
         T = x.shape[0]
+        if getattr(self, "_closed", False):
+            raise RuntimeError("this MoELayer was closed: its symmetric buffers went back to the heap")
         if T > self.max_tokens or x.shape[1] != D:
             raise ValueError(f"x must be [T <= {self.max_tokens}, {D}]")
         if x.dtype != cfg.dtype or not x.is_contiguous():

@@ -330,6 +330,8 @@ def test_layer_close_returns_its_symmetric_buffers():
         layer.close()
         layer.close()                                     # a second call is a no-op
         assert heap.bytes_in_use == used0
+        with pytest.raises(RuntimeError, match="closed"):
+            layer(x)
     # the space was reused, not appended
     cfg = MoEConfig(hidden_dim=256, ffn_dim=256, num_experts=8, topk=2)
     layer = MoELayer(cfg, max_tokens=300, heap=heap, router_std=None, debug_canaries=True)
