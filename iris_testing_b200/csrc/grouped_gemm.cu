@@ -133,6 +133,19 @@ __host__ __device__ __forceinline__ bool decode_tile(const ControlSmem& c, int G
   return true;
 }
 
+// Which tiles a scheduler (a CTA, or a CTA pair) takes: first, first + stride, ...
+// Even rounds: with R = ceil(tiles / schedulers) rounds needed anyway, only ceil(tiles / R)
+// schedulers take tiles, R each (the last ones maybe one fewer), instead of all of them taking
+// R - 1 and a few taking one more.  The makespan in tiles is the same; when the kernel streams
+// weights (few rows per expert) the last round no longer runs on a handful of SMs that cannot
+// draw the full memory bandwidth.  Schedulers past the stride sit out (first = total).
+__host__ __device__ __forceinline__ void tile_walk(int total, int schedulers, int sched_id, int& first,
+                                                   int& stride) {
+  const int rounds = (total + schedulers - 1) / schedulers;
+  stride = rounds > 0 ? (total + rounds - 1) / rounds : schedulers;
+  first = sched_id < stride ? sched_id : total;
+}
+
 // Exclusive scan of g_rows into g_row_start / g_mtile_start by one warp.
 __device__ __forceinline__ void scan_groups(ControlSmem& c, int G, int lane, int sched_rows) {
   int row_carry = 0, tile_carry = 0, sched_carry = 0;
@@ -387,6 +400,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
 
   const uint32_t tmem_base = c.tmem_base;
   const int total_tiles = c.total_sched * TN;
+  int tile_first, tile_stride;
+  tile_walk(total_tiles, sched_stride, sched_id, tile_first, tile_stride);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -400,7 +415,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
       const bool hinted = EPI != B200_EPI_ROUTER && (ga.l2_hints & 3) != 0;
       const uint64_t pol_a = (ga.l2_hints & 1) ? l2_policy_evict_last() : l2_policy_evict_normal();
       const uint64_t pol_b = (ga.l2_hints & 2) ? l2_policy_evict_first() : l2_policy_evict_normal();
-      for (int idx = sched_id; ok && idx < total_tiles; idx += sched_stride) {
+      for (int idx = tile_first; ok && idx < total_tiles; idx += tile_stride) {
         int g, m, n;
         if (!decode_tile(c, G, TN, gm, idx, cursor, g, m, n)) break;
         const int half0 = m * S::TM + static_cast<int>(cta_rank) * BM;   // first row of my half
@@ -511,7 +526,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
       uint32_t phase = 0;
       int it = 0;
       bool ok = !c.abort_flag;
-      for (int idx = sched_id; ok && idx < total_tiles; idx += sched_stride, ++it) {
+      for (int idx = tile_first; ok && idx < total_tiles; idx += tile_stride, ++it) {
         if constexpr (NT == 2) {
           // Wide tile: accumulator h takes weight rows [h*256, +256) of the tile.  Accumulator 0 must
           // be free before the first MMA; accumulator 1's MMAs may trail by up to LAG k-blocks
@@ -614,7 +629,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a0,
     int pending_arrivals = 0;   // combine epilogue: rows stored for rank `lane`, not yet published
     // accumulators are handed back on the pair leader's barrier
     const uint32_t tmem_empty_addr[2] = {map_to_cta(&c.tmem_empty[0], 0), map_to_cta(&c.tmem_empty[1], 0)};
-    for (int idx = sched_id; idx < total_tiles; idx += sched_stride, ++it) {
+    for (int idx = tile_first; idx < total_tiles; idx += tile_stride, ++it) {
       int g, m, n;
       if (!decode_tile(c, G, TN, gm, idx, cursor, g, m, n)) break;
       // NT == 1: the two accumulators alternate from tile to tile; NT == 2: both belong to this tile
@@ -1189,6 +1204,22 @@ extern "C" int b200_debug_tile_order(const int* group_rows, int G, int TN, int g
   }
   delete c;
   return written == total ? total : -2;
+}
+
+// owner[t] = the scheduler that takes tile t under tile_walk (every tile exactly once).
+extern "C" int b200_debug_tile_walk(int total, int schedulers, int* owner) {
+  if (total < 0 || schedulers < 1) return -1;
+  for (int t = 0; t < total; ++t) owner[t] = -1;
+  for (int sid = 0; sid < schedulers; ++sid) {
+    int first, stride;
+    b200::tile_walk(total, schedulers, sid, first, stride);
+    if (stride < 1) return -2;
+    for (int t = first; t < total; t += stride) {
+      if (owner[t] != -1) return -3;
+      owner[t] = sid;
+    }
+  }
+  return 0;
 }
 
 // tables: [7][world * e_local] = count, send_start, dst_row, dst_rel0, dst_mtile0, dst_rank, units

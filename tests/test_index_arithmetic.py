@@ -51,6 +51,33 @@ def test_chunks_are_evened_out():
     assert first_column[:8] == list(range(8)) and tiles[8][2] == 1
 
 
+def test_even_rounds_tile_walk_covers_every_tile_in_the_minimum_number_of_rounds():
+    """The persistent kernels' tile walk: every tile has exactly one owner, nobody takes more than
+    ceil(tiles / schedulers) tiles (the number of rounds is not increased), and the tiles are
+    spread over as few schedulers as that allows, each with a full share."""
+    lib = _lib()
+    rng = random.Random(5)
+    cases = [(0, 1), (1, 1), (1, 148), (75, 74), (896, 148), (896, 74), (128, 148), (14336, 74), (149, 148)]
+    cases += [(rng.randint(0, 3000), rng.randint(1, 148)) for _ in range(200)]
+    for total, sched in cases:
+        owner = (C.c_int * max(total, 1))()
+        assert lib.b200_debug_tile_walk(total, sched, owner) == 0, (total, sched)
+        own = list(owner)[:total]
+        assert all(0 <= o < sched for o in own), (total, sched)
+        if total == 0:
+            continue
+        rounds = -(-total // sched)
+        per = {}
+        for o in own:
+            per[o] = per.get(o, 0) + 1
+        assert max(per.values()) == rounds, (total, sched)
+        assert len(per) == -(-total // rounds) and min(per.values()) >= rounds - 1, (total, sched, len(per))
+    # the shape that motivated it: 896 tiles on 148 CTAs are 7 rounds either way; 128 CTAs take 7 each
+    owner = (C.c_int * 896)()
+    lib.b200_debug_tile_walk(896, 148, owner)
+    assert max(owner) == 127
+
+
 def dispatch_tables(lib, counts, W, EL, rank, cap):
     ET = W * EL
     flat = [counts[s][d][e] for s in range(W) for d in range(W) for e in range(EL)]
