@@ -451,7 +451,7 @@ class MoELayer(nn.Module):
         view = Plan(plan.counts, plan.bucket_start, plan.send_order[:n], plan.dst_slot[:n],
                     plan.rank_in_bucket[:n])
         if self.uses_small_path(T):
-            # 1+2. small batch: router and plan in one single-CTA launch
+            # 1+2. small batch: router and plan in one launch
             idx = torch.empty((T, k), dtype=torch.int32, device=x.device)
             wgt = torch.empty((T, k), dtype=torch.float32, device=x.device)
             bias = None if self.router_bias is None else self.router_bias.to(
