@@ -129,6 +129,9 @@ SWEEPS = {
                   for e, k in ((16, 2), (64, 2), (64, 4), (64, 8))],
     # large experts, skewed and balanced routing
     "config5": [dict(mode="layer", model="large", zipf=z, batch=8, seq=4096, experts=0, topk=0) for z in (1.2, 0.0)],
+    # the headline layer at small batches (the regime where the expert weights are streamed once per step)
+    "small": [dict(mode="layer", model="mixtral-8x7b", batch=1, seq=q, experts=0, topk=0)
+              for q in (64, 256, 512, 1024, 2048)],
 }
 
 

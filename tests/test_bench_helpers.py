@@ -97,6 +97,9 @@ def test_published_sweeps_cover_the_configurations():
     c4 = {(p["experts"], p["topk"]) for p in bench.SWEEPS["config4"]}
     assert {(e, k) for e in (8, 32, 128) for k in (1, 2, 8)} <= c4
     assert [p["zipf"] for p in bench.SWEEPS["config5"]] == [1.2, 0.0]
+    small = bench.SWEEPS["small"]
+    assert [p["batch"] * p["seq"] for p in small] == [64, 256, 512, 1024, 2048]
+    assert all(p["model"] == "mixtral-8x7b" and p["mode"] == "layer" for p in small)
 
 
 def test_vectorized_reference_packer_builds_the_reference_payload():
