@@ -233,7 +233,8 @@ route_plan_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
                         const float* __restrict__ bias, int T, int D, int E, int k, int renorm,
                         int* __restrict__ topk_idx, float* __restrict__ topk_w, int* __restrict__ counts,
                         int* __restrict__ bucket_start, int* __restrict__ send_order,
-                        int* __restrict__ dst_slot, PlanPushArgs push, int do_push, unsigned int* ticket) {
+                        int* __restrict__ dst_slot, PlanPushArgs push, int do_push, unsigned int* ticket,
+                        int wpt) {
   __shared__ float s_lg[SMALL_THREADS / 32][B200_MAX_EXPERTS];
   __shared__ short s_idx[SMALL_MAX_FLAT];
   __shared__ short s_rank[SMALL_MAX_FLAT];
@@ -244,33 +245,41 @@ route_plan_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nwarps = blockDim.x >> 5;
   const int n_flat = T * k;
   if (tid == 0) s_abort = 0;
-  // ---- router: one warp per token
-  float* lg = s_lg[warp];
+  // ---- router: `wpt` warps per token (a power of two up to the warps of the CTA; the host picks
+  // it so that a small batch still fills the SMs).  Each warp of a token takes every wpt-th group
+  // of 32 sixteen-byte pieces of the row, the partial logits meet in shared memory and the
+  // token's first warp does softmax and top-k.
   const int d16 = D / 8;
-  for (int t = blockIdx.x * nwarps + warp; t < T; t += gridDim.x * nwarps) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(t) * D);
+  const int tpc = nwarps / wpt;                       // tokens per CTA and pass
+  const int sub = warp % wpt, slot = warp / wpt;
+  for (int base = blockIdx.x * tpc; base < T; base += gridDim.x * tpc) {   // uniform per CTA
+    const int t = base + slot;
+    const bool tv = t < T;
+    const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(tv ? t : 0) * D);
     // Experts in groups of eight with independent accumulators, two 16-byte pieces of the row per
     // trip: 18 (cold) loads are in flight together instead of one dependent pair at a time.
     for (int e0 = 0; e0 < E; e0 += SMALL_EG) {
       float acc[SMALL_EG];
 #pragma unroll
       for (int j = 0; j < SMALL_EG; ++j) acc[j] = 0.f;
+      if (tv) {
 #pragma unroll 2
-      for (int i = lane; i < d16; i += 32) {
-        const uint4 xv = __ldg(xr + i);
-        uint4 wv[SMALL_EG];
+        for (int i = lane + 32 * sub; i < d16; i += 32 * wpt) {
+          const uint4 xv = __ldg(xr + i);
+          uint4 wv[SMALL_EG];
 #pragma unroll
-        for (int j = 0; j < SMALL_EG; ++j)
-          wv[j] = __ldg(reinterpret_cast<const uint4*>(wr_kmajor + static_cast<size_t>(min(e0 + j, E - 1)) * D) + i);
-        const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&xv);
+          for (int j = 0; j < SMALL_EG; ++j)
+            wv[j] = __ldg(reinterpret_cast<const uint4*>(wr_kmajor + static_cast<size_t>(min(e0 + j, E - 1)) * D) + i);
+          const __nv_bfloat162* xa = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
-        for (int j = 0; j < SMALL_EG; ++j) {
-          const __nv_bfloat162* wa = reinterpret_cast<const __nv_bfloat162*>(&wv[j]);
+          for (int j = 0; j < SMALL_EG; ++j) {
+            const __nv_bfloat162* wa = reinterpret_cast<const __nv_bfloat162*>(&wv[j]);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 a = __bfloat1622float2(xa[q]), b = __bfloat1622float2(wa[q]);
-            acc[j] = fmaf(a.x, b.x, acc[j]);
-            acc[j] = fmaf(a.y, b.y, acc[j]);
+            for (int q = 0; q < 4; ++q) {
+              const float2 a = __bfloat1622float2(xa[q]), b = __bfloat1622float2(wa[q]);
+              acc[j] = fmaf(a.x, b.x, acc[j]);
+              acc[j] = fmaf(a.y, b.y, acc[j]);
+            }
           }
         }
       }
@@ -279,44 +288,53 @@ route_plan_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16
         float a = acc[j];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
-        if (lane == 0 && e0 + j < E) lg[e0 + j] = a + (bias ? bias[e0 + j] : 0.f);
+        if (lane == 0 && e0 + j < E) s_lg[warp][e0 + j] = a;
       }
     }
-    __syncwarp();
-    float mx = -INFINITY;
-    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    float sum = 0.f;
-    for (int e = lane; e < E; e += 32) sum += __expf(lg[e] - mx);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    TopK tk; tk.init();
-    for (int e = lane; e < E; e += 32) tk.push(lg[e], e);
-    float wsum = 0.f, my_w = 0.f;
-    int my_i = 0;
-    for (int r = 0; r < k; ++r) {
-      float bv = tk.v[0]; int bi = tk.i[0] < 0 ? 0x7fffffff : tk.i[0];
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    __syncthreads();                                  // every warp's partial logits are in place
+    if (tv && sub == 0) {
+      float* lg = s_lg[warp];
+      for (int e = lane; e < E; e += 32) {
+        float v = bias ? bias[e] : 0.f;
+        for (int s2 = 0; s2 < wpt; ++s2) v += s_lg[warp + s2][e];
+        lg[e] = v;
       }
-      if (tk.i[0] == bi) {   // the winning lane pops its head
+      __syncwarp();
+      float mx = -INFINITY;
+      for (int e = lane; e < E; e += 32) mx = fmaxf(mx, lg[e]);
 #pragma unroll
-        for (int j = 0; j < ROUTER_MAX_K - 1; ++j) { tk.v[j] = tk.v[j + 1]; tk.i[j] = tk.i[j + 1]; }
-        tk.v[ROUTER_MAX_K - 1] = -INFINITY; tk.i[ROUTER_MAX_K - 1] = -1;
+      for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float sum = 0.f;
+      for (int e = lane; e < E; e += 32) sum += __expf(lg[e] - mx);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      TopK tk; tk.init();
+      for (int e = lane; e < E; e += 32) tk.push(lg[e], e);
+      float wsum = 0.f, my_w = 0.f;
+      int my_i = 0;
+      for (int r = 0; r < k; ++r) {
+        float bv = tk.v[0]; int bi = tk.i[0] < 0 ? 0x7fffffff : tk.i[0];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (tk.i[0] == bi) {   // the winning lane pops its head
+#pragma unroll
+          for (int j = 0; j < ROUTER_MAX_K - 1; ++j) { tk.v[j] = tk.v[j + 1]; tk.i[j] = tk.i[j + 1]; }
+          tk.v[ROUTER_MAX_K - 1] = -INFINITY; tk.i[ROUTER_MAX_K - 1] = -1;
+        }
+        const float p = __expf(bv - mx) / sum;
+        wsum += p;
+        if (lane == r) { my_w = p; my_i = bi; }
       }
-      const float p = __expf(bv - mx) / sum;
-      wsum += p;
-      if (lane == r) { my_w = p; my_i = bi; }
+      if (lane < k) {
+        topk_idx[static_cast<size_t>(t) * k + lane] = my_i;
+        topk_w[static_cast<size_t>(t) * k + lane] = renorm ? my_w / wsum : my_w;
+      }
     }
-    if (lane < k) {
-      topk_idx[static_cast<size_t>(t) * k + lane] = my_i;
-      topk_w[static_cast<size_t>(t) * k + lane] = renorm ? my_w / wsum : my_w;
-    }
-    __syncwarp();
+    __syncthreads();                                  // the partial-logit rows are reused by the next pass
   }
   // ---- hand-over: every CTA publishes its choices and takes a ticket; the last one plans
   __threadfence();
@@ -538,11 +556,15 @@ extern "C" int b200_route_plan_small(const void* x, const void* wr_kmajor, const
   b200::PlanPushArgs pz;
   memset(&pz, 0, sizeof(pz));
   const int warps = b200::SMALL_THREADS / 32;
-  const int grid = std::max(1, std::min((T + warps - 1) / warps, 148));
+  // warps per token: as many as still leave every token of the batch a place on the 148 SMs
+  int wpt = warps;
+  while (wpt > 1 && static_cast<long long>(T) * wpt > 148LL * warps) wpt >>= 1;
+  const int tpc = warps / wpt;
+  const int grid = std::max(1, std::min((T + tpc - 1) / tpc, 148));
   b200::route_plan_small_kernel<<<grid, b200::SMALL_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(wr_kmajor), bias, T, D, E, k,
       renorm, topk_idx, topk_w, counts, bucket_start, send_order, dst_slot, push ? *push : pz, push ? 1 : 0,
-      ticket);
+      ticket, wpt);
   b200_count_launches(1);
   return static_cast<int>(cudaGetLastError());
 }
