@@ -216,10 +216,10 @@ __global__ void plan_finalize_kernel(const int* __restrict__ topk_idx,
 // ---------------------------------------------------------------------------
 // Small-token path: router AND plan in ONE launch (instead of three launches).
 // For a few thousand routed copies the layer is launch- and latency-bound, and the router GEMM on
-// tensor cores (TMEM allocation, barriers, 148 CTAs) costs more than the arithmetic.  Here one warp
-// per token forms the logits with 16-byte loads from the K-major router weights (tokens spread
-// over as many CTAs as there are groups of eight tokens, so that the cold loads of a wide hidden
-// dimension run in parallel), the same softmax / top-k code picks the experts, and the CTA that
+// tensor cores (TMEM allocation, barriers, 148 CTAs) costs more than the arithmetic.  Here one to
+// eight warps per token form the logits with 16-byte loads from the K-major router weights (the
+// tokens spread over up to 148 CTAs, so that the cold loads of a wide hidden dimension run in
+// parallel), the same softmax / top-k code picks the experts, and the CTA that
 // finishes LAST (a ticket in global memory; nobody waits) builds the plan in shared memory
 // (stable ranks per expert by ballot, scan, send order) and pushes the counts to the peers.
 // Limits (checked by the launcher): n_flat <= SMALL_MAX_FLAT, experts <= B200_MAX_EXPERTS.
