@@ -237,3 +237,25 @@ def test_zero_padding_clears_stale_rows_only():
         for s_ in range(3):
             n = int(pca[e, s_])
             assert bool((buf[e, s_, :n] == 1).all()) and bool((buf[e, s_, n:] == 0).all())
+
+
+def test_small_token_path_rule():
+    """Which batches take the one-launch router + plan: at most 4096 routed copies and at most 16
+    load trips per router warp (decided on the host from the shape alone)."""
+    from iris_testing_b200.config import MoEConfig
+    from iris_testing_b200.models import MoELayer
+
+    def layer(D, E, k):
+        # tiny weights: the rule only reads the configuration
+        return MoELayer(MoEConfig(hidden_dim=D, ffn_dim=128, num_experts=E, topk=k), max_tokens=8, router_std=None)
+
+    mixtral = layer(4096, 8, 2)
+    assert [mixtral.uses_small_path(T) for T in (0, 1, 64, 2048, 2049, 16384)] == [True, True, True, True, False, False]
+    assert mixtral.launches_for(64) == 4 and mixtral.launches_for(16384) == 6
+    fine = layer(2048, 64, 8)
+    assert not fine.uses_small_path(512) and not fine.uses_small_path(513)     # 8 expert groups x 4 row pieces
+    assert layer(256, 64, 8).uses_small_path(512)
+    tiny = layer(256, 8, 2)
+    assert tiny.uses_small_path(64) and tiny.uses_small_path(2048) and not tiny.uses_small_path(2049)
+    mixtral.small_path = False
+    assert not mixtral.uses_small_path(64) and mixtral.launches_for(64) == 6
